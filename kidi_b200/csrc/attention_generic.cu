@@ -1,0 +1,246 @@
+// Per-head RMSNorm + rotary encoding + cache write, and attention over the cache
+// for any element type, head size and number of heads.
+//
+// Formulas (reference):
+//  * fused per-head norm and rotation, norm before rotation, half-split pairing:
+//      n_c = x_c * (1/sqrt(sum(x^2)/d + eps)) * w_c
+//      out_c = n_c * cos[pos, c mod half] + r_c * sin[pos, c mod half],
+//      r_c = -n_{c+half} for c < half, n_{c-half} otherwise
+//    (src/kidi/layers/qwen3.cpp:37-48, src/kidi/ops/context.cpp:1051-1065,
+//     src/kidi/runtime/mps/eager_kernels.metal:87-97)
+//  * scores s = (q . k) * scale, key head = query head / (heads / kv_heads), softmax
+//    over the visible keys, output = sum p_u v_u
+//    (src/kidi/layers/qwen3.cpp:53-54, src/kidi/runtime/vulkan/attention.comp:32-101)
+//  * the causal rule is the generic causal path's: key u is visible to the query at
+//    position p when u <= p (src/kidi/model/gemma4.cpp:736-740); with a window W,
+//    when also u > p - W.
+// Norm sums, rotation, scores, softmax and the weighted sum are 32-bit.
+#include "common.cuh"
+
+struct RopeStoreArgs {
+    void* qkv;                 // [rows, ld] : q heads, then k heads, then v heads, each head_dim wide
+    long long ld;
+    const void* q_norm;        // [head_dim] or null
+    const void* k_norm;        // [head_dim] or null
+    const float* cos_table;    // [positions, rotary_dim/2] or null (no rotation)
+    const float* sin_table;
+    const int* row_seq;        // [rows]  (-1: padding row, skipped)
+    const int* row_pos;        // [rows]
+    const int* seq_slot;       // [seqs]
+    const int* seq_start;      // [seqs]
+    const int* seq_len;        // [seqs]
+    void* k_cache;             // storage of this schedule entry, or null (no write)
+    void* v_cache;
+    CacheGeometry cache;
+    int rows, heads, kv_heads, head_dim, rotary_dim;
+    float eps;
+    int transform;             // 0: only copy the k and v heads, as they are, to the cache
+};
+
+// One warp per (row, head) over heads + 2*kv_heads heads.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) rope_store_kernel(RopeStoreArgs a) {
+    __shared__ float normed[4][256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_heads = a.heads + 2 * a.kv_heads;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)a.rows * total_heads) return;
+    const int row = (int)(item / total_heads);
+    const int head = (int)(item - (long long)row * total_heads);
+    const int seq = a.row_seq[row];
+    if (seq < 0) return;
+    const int position = a.row_pos[row];
+    const int d = a.head_dim;
+    T* vector = (T*)a.qkv + row * a.ld + (long long)head * d;
+
+    // Where this head goes in the cache, if anywhere.
+    T* cached = nullptr;
+    if (head >= a.heads && a.k_cache) {
+        bool keep = true;
+        if (a.cache.ring_pages) {  // a ring keeps the last ring_tokens tokens of the step only
+            const int ring_tokens = a.cache.ring_pages << a.cache.page_shift;
+            keep = position >= a.seq_start[seq] + a.seq_len[seq] - ring_tokens;
+        }
+        if (keep) {
+            const bool is_key = head < a.heads + a.kv_heads;
+            const int kv_head = is_key ? head - a.heads : head - a.heads - a.kv_heads;
+            cached = (T*)(is_key ? a.k_cache : a.v_cache) +
+                     cache_row_offset(a.cache, a.seq_slot[seq], position, kv_head);
+        }
+    }
+
+    if (head >= a.heads + a.kv_heads || !a.transform) {  // a value head, or copy only
+        if (cached)
+            for (int c = lane; c < d; c += 32) cached[c] = vector[c];
+        return;
+    }
+
+    const TW* weight = (const TW*)(head < a.heads ? a.q_norm : a.k_norm);
+    float values[8];
+    float square = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        values[i] = c < d ? to_float(vector[c]) : 0.f;
+        square = fmaf(values[i], values[i], square);
+    }
+    float inv = 1.f;
+    if (weight) inv = 1.0f / sqrtf(warp_sum(square) / (float)d + a.eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d) {
+            if (weight) values[i] = values[i] * inv * to_float(weight[c]);
+            normed[warp][c] = values[i];
+        }
+    }
+    __syncwarp();
+    const int half = a.rotary_dim / 2;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        if (c >= d) continue;
+        float out = values[i];
+        if (a.cos_table && c < a.rotary_dim) {
+            const int j = c < half ? c : c - half;
+            const float cosine = a.cos_table[(long long)position * half + j];
+            const float sine = a.sin_table[(long long)position * half + j];
+            const float rotated = c < half ? -normed[warp][c + half] : normed[warp][c - half];
+            out = values[i] * cosine + rotated * sine;
+        }
+        const T stored = from_float<T>(out);
+        vector[c] = stored;
+        if (cached) cached[c] = stored;
+    }
+}
+
+KIDI_API int kidi_rope_store(const RopeStoreArgs* args, int dtype, int norm_dtype, cudaStream_t stream) {
+    const RopeStoreArgs& a = *args;
+    if (a.rows <= 0) return 0;
+    if (a.head_dim > 256 || a.head_dim <= 0 || a.rotary_dim > a.head_dim || (a.rotary_dim & 1)) return KIDI_REFUSED_SIZE;
+    const long long items = (long long)a.rows * (a.heads + 2 * a.kv_heads);
+    const unsigned blocks = (unsigned)((items + 3) / 4);
+    if (dtype == KIDI_F32 && norm_dtype == KIDI_F32) rope_store_kernel<float, float><<<blocks, 128, 0, stream>>>(a);
+    else if (dtype == KIDI_F32 && norm_dtype == KIDI_BF16) rope_store_kernel<float, bf16><<<blocks, 128, 0, stream>>>(a);
+    else if (dtype == KIDI_BF16 && norm_dtype == KIDI_F32) rope_store_kernel<bf16, float><<<blocks, 128, 0, stream>>>(a);
+    else if (dtype == KIDI_BF16 && norm_dtype == KIDI_BF16) rope_store_kernel<bf16, bf16><<<blocks, 128, 0, stream>>>(a);
+    else return KIDI_REFUSED_DTYPE;
+    return kidi_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+struct AttentionArgs {
+    const void* q;        // [rows, ldq], head h at h*head_dim
+    long long ldq;
+    const void* k_step;   // keys of this step's rows [rows, ldkv], kv head g at g*head_dim; null: read the cache only
+    const void* v_step;
+    long long ldkv;
+    const void* k_cache;  // storage of this schedule entry (may be null when every key is in the step)
+    const void* v_cache;
+    CacheGeometry cache;
+    void* out;            // [rows, ldo]
+    long long ldo;
+    const int* row_seq;   // [rows] (-1: padding row: output zeros)
+    const int* row_pos;
+    const int* seq_slot;
+    const int* seq_start; // tokens in the cache before this step
+    const int* seq_row0;  // first packed row of the sequence
+    int rows, heads, kv_heads, head_dim, window;  // window 0: every earlier key is visible
+    float scale;
+};
+
+// One block of 4 warps per (row, head). Warp w takes keys lo+w, lo+w+4, ... in
+// ascending order with an online softmax; the four partial results are merged in
+// warp order. The order depends on the row's position and window only, so a row's
+// result is the same in every batch and under every cut of the work.
+template <typename T>
+__global__ void __launch_bounds__(128) attention_generic_kernel(AttentionArgs a) {
+    __shared__ float query[256];
+    __shared__ float part_acc[4][256];
+    __shared__ float part_max[4], part_sum[4];
+    const int row = blockIdx.x, head = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int d = a.head_dim;
+    T* out = (T*)a.out + row * a.ldo + (long long)head * d;
+    const int seq = a.row_seq[row];
+    if (seq < 0) {
+        for (int c = threadIdx.x; c < d; c += 128) out[c] = from_float<T>(0.f);
+        return;
+    }
+    const int position = a.row_pos[row];
+    const int first = a.window > 0 ? max(0, position - a.window + 1) : 0;
+    const int kv_head = head / (a.heads / a.kv_heads);
+    const int slot = a.seq_slot[seq];
+    const int start = a.k_step ? a.seq_start[seq] : 0x7fffffff;  // keys >= start come from the step
+    const int row0 = a.seq_row0[seq];
+    const T* q = (const T*)a.q + row * a.ldq + (long long)head * d;
+    for (int c = threadIdx.x; c < d; c += 128) query[c] = to_float(q[c]);
+    __syncthreads();
+
+    float best = -INFINITY, denom = 0.f;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int u = first + warp; u <= position; u += 4) {
+        const T *key, *value;
+        if (u >= start) {
+            const long long offset = (long long)(row0 + u - start) * a.ldkv + (long long)kv_head * d;
+            key = (const T*)a.k_step + offset;
+            value = (const T*)a.v_step + offset;
+        } else {
+            const long long offset = cache_row_offset(a.cache, slot, u, kv_head);
+            key = (const T*)a.k_cache + offset;
+            value = (const T*)a.v_cache + offset;
+        }
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = lane + 32 * i;
+            if (c < d) dot = fmaf(query[c], to_float(key[c]), dot);
+        }
+        const float score = warp_sum(dot) * a.scale;
+        const float next = fmaxf(best, score);
+        const float keep = expf(best - next);  // 0 on the first key (best = -inf)
+        const float weight = expf(score - next);
+        denom = denom * keep + weight;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = lane + 32 * i;
+            if (c < d) acc[i] = acc[i] * keep + weight * to_float(value[c]);
+        }
+        best = next;
+    }
+    if (lane == 0) { part_max[warp] = best; part_sum[warp] = denom; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d) part_acc[warp][c] = acc[i];
+    }
+    __syncthreads();
+    float top = part_max[0];
+#pragma unroll
+    for (int w = 1; w < 4; ++w) top = fmaxf(top, part_max[w]);
+    float total = 0.f, factor[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        factor[w] = part_max[w] == -INFINITY ? 0.f : expf(part_max[w] - top);
+        total += part_sum[w] * factor[w];
+    }
+    for (int c = threadIdx.x; c < d; c += 128) {
+        float value = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) value += part_acc[w][c] * factor[w];
+        out[c] = from_float<T>(value / total);
+    }
+}
+
+KIDI_API int kidi_attention_generic(const AttentionArgs* args, int dtype, cudaStream_t stream) {
+    const AttentionArgs& a = *args;
+    if (a.rows <= 0) return 0;
+    if (a.head_dim > 256 || a.head_dim <= 0 || a.heads % a.kv_heads || a.heads > 65535) return KIDI_REFUSED_SIZE;
+    dim3 grid(a.rows, a.heads);
+    if (dtype == KIDI_F32) attention_generic_kernel<float><<<grid, 128, 0, stream>>>(a);
+    else if (dtype == KIDI_BF16) attention_generic_kernel<bf16><<<grid, 128, 0, stream>>>(a);
+    else return KIDI_REFUSED_DTYPE;
+    return kidi_launch_status();
+}

@@ -1,0 +1,131 @@
+// Embedding gather, residual-add + RMSNorm, and the SiLU gate.
+//
+// Formulas (reference): embedding row gather times a scalar scale
+// (src/kidi/layers/gemma4.cpp:97-99,132-142); RMSNorm y = x * (1/sqrt(sum(x^2)/H + eps)) * w
+// (src/kidi/runtime/mps/eager_kernels.metal:65-87); SiLU gate f = g / (1 + exp(-g)) * u
+// (src/kidi/runtime/mps/eager_kernels.metal:129-137). The residual stream is kept in
+// 32-bit in every engine dtype, and the sum of squares and the inverse root are 32-bit.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+template <typename TW>
+__global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                                 const int* __restrict__ tokens, int hidden, int vocab, float scale) {
+    const int row = blockIdx.x;
+    const int token = tokens[row];
+    float* destination = out + (long long)row * hidden;
+    if (token < 0 || token >= vocab) {  // never read outside the table
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) destination[c] = 0.f;
+        return;
+    }
+    const TW* source = table + (long long)token * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) destination[c] = to_float(source[c]) * scale;
+}
+
+KIDI_API int kidi_embedding(float* out, const void* table, int table_dtype, const int* tokens, int rows, int hidden,
+                            int vocab, float scale, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == KIDI_F32)
+        embedding_kernel<float><<<rows, threads, 0, stream>>>(out, (const float*)table, tokens, hidden, vocab, scale);
+    else if (table_dtype == KIDI_BF16)
+        embedding_kernel<bf16><<<rows, threads, 0, stream>>>(out, (const bf16*)table, tokens, hidden, vocab, scale);
+    else
+        return KIDI_REFUSED_DTYPE;
+    return kidi_launch_status();
+}
+
+// ------------------------------------------------------- residual add + RMSNorm
+// One block per output row r. Source row s = row_index ? row_index[r] : r.
+//   v = residual[s] + delta[s]   (delta optional)
+//   if write_residual: residual[s] = v
+//   y[r] = v * inv * w,  inv = 1 / sqrt(mean(v^2) + eps)
+// The row is staged in shared memory so that it is read once.
+template <typename TD, typename TW, typename TY, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const TW* __restrict__ weight,
+                   TY* __restrict__ y, const int* __restrict__ row_index, int hidden, float eps, int write_residual) {
+    extern __shared__ float staged[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long long s = row_index ? row_index[r] : r;
+    float* h = residual + s * hidden;
+    float square = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += THREADS) {
+        float value = h[c];
+        if (delta) value += to_float(delta[s * hidden + c]);
+        if (write_residual) h[c] = value;
+        staged[c] = value;
+        square = fmaf(value, value, square);
+    }
+    const float total = block_sum<THREADS>(square, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    TY* out = y + (long long)r * hidden;
+    for (int c = threadIdx.x; c < hidden; c += THREADS)
+        out[c] = from_float<TY>(staged[c] * inv * to_float(weight[c]));
+}
+
+template <typename TD, typename TW, typename TY>
+static int launch_add_rmsnorm(float* residual, const void* delta, const void* weight, void* y, const int* row_index,
+                              int rows, int hidden, float eps, int write_residual, cudaStream_t stream) {
+    constexpr int THREADS = 256;
+    const size_t shared = (size_t)hidden * sizeof(float);
+    if (shared > 200 * 1024) return KIDI_REFUSED_SIZE;
+    auto kernel = add_rmsnorm_kernel<TD, TW, TY, THREADS>;
+    if (shared > 48 * 1024) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (status != cudaSuccess) return (int)status;
+    }
+    kernel<<<rows, THREADS, shared, stream>>>(residual, (const TD*)delta, (const TW*)weight, (TY*)y, row_index,
+                                               hidden, eps, write_residual);
+    return kidi_launch_status();
+}
+
+// delta_dtype may be KIDI_NONE (no delta). The residual is always float.
+KIDI_API int kidi_add_rmsnorm(float* residual, const void* delta, int delta_dtype, const void* weight,
+                              int weight_dtype, void* y, int y_dtype, const int* row_index, int rows, int hidden,
+                              float eps, int write_residual, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (delta_dtype == KIDI_NONE) { delta = nullptr; delta_dtype = KIDI_F32; }
+#define KIDI_CASE(D, TD, W, TW, Y, TY)                                                                     \
+    if (delta_dtype == D && weight_dtype == W && y_dtype == Y)                                             \
+        return launch_add_rmsnorm<TD, TW, TY>(residual, delta, weight, y, row_index, rows, hidden, eps,    \
+                                              write_residual, stream);
+    KIDI_CASE(KIDI_F32, float, KIDI_F32, float, KIDI_F32, float)
+    KIDI_CASE(KIDI_F32, float, KIDI_F32, float, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16, KIDI_F32, float)
+    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float, KIDI_F32, float)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16, KIDI_F32, float)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16, KIDI_BF16, bf16)
+#undef KIDI_CASE
+    return KIDI_REFUSED_DTYPE;
+}
+
+// ------------------------------------------------------------------ SiLU gate
+// gate_up [rows, 2*inter] (gate = first inter columns, up = last inter) -> out [rows, inter]
+template <typename T>
+__global__ void silu_gate_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const long long row = index / inter;
+    const int c = (int)(index - row * inter);
+    const float gate = to_float(gate_up[row * 2 * inter + c]);
+    const float up = to_float(gate_up[row * 2 * inter + inter + c]);
+    out[index] = from_float<T>(gate / (1.0f + expf(-gate)) * up);
+}
+
+KIDI_API int kidi_silu_gate(const void* gate_up, void* out, int dtype, int rows, int inter, cudaStream_t stream) {
+    const long long total = (long long)rows * inter;
+    if (total <= 0) return 0;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (dtype == KIDI_F32)
+        silu_gate_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, inter);
+    else if (dtype == KIDI_BF16)
+        silu_gate_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, inter);
+    else
+        return KIDI_REFUSED_DTYPE;
+    return kidi_launch_status();
+}

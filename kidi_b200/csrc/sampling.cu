@@ -1,0 +1,134 @@
+// Token selection on the device: greedy argmax and temperature sampling.
+//
+// Greedy follows the reference's rules: the largest logit wins, ties go to the lowest
+// index, and a row that holds a NaN or +infinity, or no finite value at all, selects
+// -1, which the generation loop rejects (ARCHITECTURE.md:612-616,
+// src/kidi/runtime/mps/eager_kernels.metal:30-50, src/kidi/inference/decoder.cpp:72-78).
+// Temperature sampling is this library's own (the reference samples text greedily
+// only): p = softmax(logits / T) in 32-bit, then the inverse of the cumulative
+// distribution in index order at a uniform number u that depends on (seed, sequence
+// key, step) only, so a sequence draws the same tokens in any batch.
+#include "common.cuh"
+
+namespace {
+constexpr int THREADS = 256;
+
+struct Best {
+    float value;
+    int index;
+};
+
+__device__ __forceinline__ Best better(Best a, Best b) {
+    if (b.value > a.value || (b.value == a.value && b.index < a.index)) return b;
+    return a;
+}
+
+// Returns the row's argmax to every thread; index -1 for an invalid row.
+__device__ Best block_argmax(const float* row, int vocab, float inverse_temperature, Best* scratch, int* invalid) {
+    Best best{-INFINITY, 0x7fffffff};
+    bool bad = false;
+    for (int c = threadIdx.x; c < vocab; c += THREADS) {
+        const float value = row[c];
+        bad |= isnan(value) || value == INFINITY;
+        if (value > best.value) best = Best{value, c};  // ascending c: the first maximum stays
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, best.value, offset), __shfl_xor_sync(0xffffffffu, best.index, offset)};
+        best = better(best, other);
+    }
+    if (threadIdx.x == 0) *invalid = 0;
+    __syncthreads();
+    if (bad) atomicOr(invalid, 1);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = best;
+    __syncthreads();
+    best = scratch[0];
+#pragma unroll
+    for (int w = 1; w < THREADS / 32; ++w) best = better(best, scratch[w]);
+    if (*invalid || best.value == -INFINITY) best.index = -1;
+    (void)inverse_temperature;
+    return best;
+}
+
+__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out,
+                                                         int vocab) {
+    __shared__ Best scratch[THREADS / 32];
+    __shared__ int invalid;
+    const Best best = block_argmax(logits + (long long)blockIdx.x * vocab, vocab, 1.f, scratch, &invalid);
+    if (threadIdx.x == 0) out[blockIdx.x] = best.index;
+}
+
+// 64-bit mix (splitmix64 finaliser) of the three keys; 24 random bits -> u in [0, 1).
+__device__ __forceinline__ float uniform_from(unsigned long long seed, unsigned long long key,
+                                              unsigned long long step) {
+    unsigned long long z = seed * 0x9E3779B97F4A7C15ull + key * 0xBF58476D1CE4E5B9ull + step * 0x94D049BB133111EBull +
+                           0x2545F4914F6CDD1Dull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+// One block per row. Thread t owns the contiguous chunk [t*chunk, (t+1)*chunk) of the
+// vocabulary, so that the cumulative sum runs in index order.
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, const float* __restrict__ temperature,
+              unsigned long long seed, const long long* __restrict__ keys, const int* __restrict__ steps) {
+    __shared__ Best scratch[THREADS / 32];
+    __shared__ int invalid;
+    __shared__ float sums[THREADS];
+    __shared__ float reduce[32];
+    const int r = blockIdx.x;
+    const float* row = logits + (long long)r * vocab;
+    const Best best = block_argmax(row, vocab, 1.f, scratch, &invalid);
+    const float t = temperature[r];
+    if (best.index < 0 || !(t > 0.f)) {  // greedy, or nothing to draw from
+        if (threadIdx.x == 0) out[r] = best.index;
+        return;
+    }
+    const float inverse = 1.0f / t;
+    const int chunk = (vocab + THREADS - 1) / THREADS;
+    const int begin = min(vocab, (int)threadIdx.x * chunk), end = min(vocab, begin + chunk);
+    float mine = 0.f;
+    for (int c = begin; c < end; ++c) mine += expf((row[c] - best.value) * inverse);
+    sums[threadIdx.x] = mine;
+    const float total = block_sum<THREADS>(mine, reduce);
+    const float target = uniform_from(seed, (unsigned long long)keys[r], (unsigned long long)steps[r]) * total;
+    __syncthreads();
+    // The owner of the target: the first thread whose inclusive prefix exceeds it.
+    if (threadIdx.x == 0) {
+        float before = 0.f;
+        int owner = THREADS - 1;
+        for (int w = 0; w < THREADS; ++w) {
+            if (before + sums[w] > target) { owner = w; break; }
+            before += sums[w];
+        }
+        // Walk the owner's chunk.
+        const int first = min(vocab, owner * chunk), last = min(vocab, first + chunk);
+        int chosen = -1;
+        float running = before;
+        for (int c = first; c < last; ++c) {
+            const float p = expf((row[c] - best.value) * inverse);
+            running += p;
+            if (p > 0.f) chosen = c;          // the last token with mass, should rounding leave the target beyond
+            if (running > target) { chosen = c; break; }
+        }
+        out[r] = chosen >= 0 ? chosen : best.index;
+    }
+}
+}  // namespace
+
+KIDI_API int kidi_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0) return KIDI_REFUSED_SIZE;
+    argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, out, vocab);
+    return kidi_launch_status();
+}
+
+KIDI_API int kidi_sample(const float* logits, int* out, int rows, int vocab, const float* temperature,
+                         unsigned long long seed, const long long* keys, const int* steps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0) return KIDI_REFUSED_SIZE;
+    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, out, vocab, temperature, seed, keys, steps);
+    return kidi_launch_status();
+}

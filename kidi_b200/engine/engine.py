@@ -1,0 +1,165 @@
+"""The engine: a loaded model, its cache, and the one step function.
+
+`Engine.step(batch)` is everything between a request's tokens and its next token's
+logits. It runs only the tokens it is given, as one packed batch, against what
+earlier steps left in the cache, and returns the logits at the wanted places. It is
+the reference's generic causal contract folded into one call: `prefill`, `forward`
+and `forward_batch_tokens` of src/kidi/model/model.h:106-150, with the step of
+src/kidi/model/gemma4.cpp:981-1069 as the model for its order (validate, embed, per
+layer write the cache and attend, head at the wanted rows, advance the positions
+only when everything succeeded).
+"""
+from __future__ import annotations
+
+import dataclasses
+import time
+from typing import Any, Dict, List, Mapping, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.sequence_cache import SequenceCache
+from ..config.reader import read_config_json
+from ..errors import KidiError, invalid_argument, runtime_error
+from ..kernels import attention as attention_kernels
+from ..registry import spec_from_config
+from ..weights.loader import Checkpoint, TensorDict, bind_parameters
+from ..weights.random_init import random_parameters
+from .model import CausalLM
+from .plan import StepBatch, StepPlan, build_plan
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+          torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+class DeviceTables:
+    """The integer tables of a `StepPlan` on the device, as views of one buffer."""
+
+    def __init__(self, buffer: torch.Tensor, offsets: Mapping[str, tuple]):
+        for name, (begin, size) in offsets.items():
+            setattr(self, name, buffer[begin:begin + size])
+
+
+class StepContext:
+    """What parts see of a step."""
+
+    def __init__(self, plan: StepPlan, tables: DeviceTables, cache: SequenceCache, dtype: torch.dtype,
+                 device: torch.device):
+        self.plan, self.tables, self.cache, self.dtype, self.device = plan, tables, cache, dtype, device
+
+    def attention(self, qkv, out, **arguments) -> None:
+        attention_kernels.run(self, qkv, out, **arguments)
+
+
+class Engine:
+    def __init__(self, model: CausalLM, *, max_tokens: int, max_slots: Optional[int] = None, config: Any = None):
+        if not torch.cuda.is_available() or model.env.device.type != "cuda":
+            raise runtime_error("this engine runs on a CUDA device (sm_100a); none is available")
+        if not model.loaded:
+            raise invalid_argument("the model has no weights yet")
+        self.model = model
+        self.config = config
+        self.spec = model.spec
+        self.dtype, self.device = model.env.dtype, model.env.device
+        self.vocab_size = model.spec.vocab_size
+        self.cache = SequenceCache(model.cache_requests(), max_tokens=max_tokens,
+                                   max_positions=model.spec.max_positions, dtype=self.dtype, device=self.device,
+                                   max_slots=max_slots, cache_from=model.cache_sources())
+        self._staging = [None, None]      # pinned host buffers, used in turn
+        self._staging_done = [None, None]  # events: the copy out of the buffer has finished
+        self._turn = 0
+        self._tables_buffer: Optional[torch.Tensor] = None
+
+    # ---------------------------------------------------------------- loading
+    @classmethod
+    def load(cls, model_dir: str, *, dtype="bfloat16", device="cuda:0", max_tokens: int = 4096,
+             max_slots: Optional[int] = None) -> "Engine":
+        """From a folder with config.json and model.safetensors; config.json chooses the model."""
+        engine_dtype = _dtype(dtype)
+        _require_cuda(device)
+        _, typed, spec = spec_from_config(read_config_json(model_dir))
+        model = CausalLM(spec, engine_dtype, torch.device(device))
+        checkpoint = Checkpoint(model_dir)
+        try:
+            with torch.cuda.device(model.env.device):
+                model.bind(bind_parameters(model.parameters(), checkpoint, engine_dtype=engine_dtype,
+                                           device=model.env.device, ignored=spec.ignored_tensors))
+        finally:
+            checkpoint.close()
+        return cls(model, max_tokens=max_tokens, max_slots=max_slots, config=typed)
+
+    @classmethod
+    def from_config(cls, config: Mapping[str, Any], *, seed: int = 0, dtype="bfloat16", device="cuda:0",
+                    max_tokens: int = 4096, max_slots: Optional[int] = None,
+                    tensors: Optional[Mapping[str, torch.Tensor]] = None) -> "Engine":
+        """From a config.json dictionary, with random weights drawn on the device from
+        `seed`, or with the checkpoint tensors given in `tensors`."""
+        engine_dtype = _dtype(dtype)
+        _require_cuda(device)
+        _, typed, spec = spec_from_config(config)
+        model = CausalLM(spec, engine_dtype, torch.device(device))
+        with torch.cuda.device(model.env.device):
+            if tensors is not None:
+                bound = bind_parameters(model.parameters(), TensorDict(tensors), engine_dtype=engine_dtype,
+                                        device=model.env.device, ignored=spec.ignored_tensors)
+            else:
+                bound = random_parameters(model.parameters(), seed, engine_dtype, model.env.device)
+            model.bind(bound)
+        return cls(model, max_tokens=max_tokens, max_slots=max_slots, config=typed)
+
+    # ------------------------------------------------------------------ slots
+    def acquire(self) -> int:
+        return self.cache.acquire()
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    # ------------------------------------------------------------------- step
+    def _upload(self, plan: StepPlan) -> DeviceTables:
+        packed = plan.packed()
+        turn = self._turn
+        self._turn ^= 1
+        if self._staging_done[turn] is not None:
+            self._staging_done[turn].synchronize()
+        staging = self._staging[turn]
+        if staging is None or staging.numel() < packed.size:
+            staging = torch.empty(max(1024, 2 * packed.size), dtype=torch.int32).pin_memory()
+            self._staging[turn] = staging
+        staging[:packed.size].copy_(torch.from_numpy(packed))
+        buffer = torch.empty(packed.size, dtype=torch.int32, device=self.device)
+        buffer.copy_(staging[:packed.size], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._staging_done[turn] = event
+        return DeviceTables(buffer, plan.offsets())
+
+    def step(self, batch: StepBatch) -> torch.Tensor:
+        """Runs one step and returns float32 logits [wanted places, vocab] on the
+        device, in the order of the batch's sequences and of their `want` lists."""
+        with torch.cuda.device(self.device):
+            starts = [self.cache.length(slot) for slot in batch.slots]
+            plan = build_plan(batch, starts, self.vocab_size)
+            growth = [(slot, start + int(count)) for slot, start, count in zip(batch.slots, starts, plan.seq_len)]
+            self.cache.reserve(growth)
+            self.cache.flush_tables()
+            ctx = StepContext(plan, self._upload(plan), self.cache, self.dtype, self.device)
+            logits = self.model.forward(ctx)
+            self.cache.commit(growth)
+            return logits
+
+    # ------------------------------------------------------------- accounting
+    def memory(self) -> Dict[str, int]:
+        return {"weight_bytes": self.model.weight_bytes, "cache_bytes": self.cache.bytes()}
+
+
+def _require_cuda(device) -> None:
+    if torch.device(device).type != "cuda" or not torch.cuda.is_available():
+        raise runtime_error(f"this engine runs on a CUDA device (sm_100a) and has no CPU path; "
+                            f"device '{device}' cannot be used here")
+
+
+def _dtype(name) -> torch.dtype:
+    try:
+        return DTYPES[name]
+    except KeyError:
+        raise invalid_argument(f"dtype must be bfloat16 or float32, not {name!r}") from None

@@ -1,0 +1,108 @@
+"""Grouped-query attention as a mixer.
+
+The reference's Qwen3 attention (src/kidi/layers/qwen3.cpp:13-56): one fused
+projection to q, k and v heads; an optional per-head RMSNorm on q and k followed by
+rotary encoding (norm before rotation, one weight vector for all heads); scores
+scaled by 1/sqrt(head_dim); query head h reads key/value head h // (heads/kv_heads);
+an output projection. What this part adds is the causal rule, an optional window
+and the cache: key u is visible from position p when u <= p and, with a window W,
+u > p - W.
+
+Parameters (`spec.params`): hidden_size, num_heads, num_kv_heads, head_dim, qk_norm
+(bool), qk_norm_eps, position (name of a rotary encoding in `env.positions`, or None),
+window (tokens, or None), scale (None: 1/sqrt(head_dim)).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from ..cache.sequence_cache import KVRequest
+from ..errors import invalid_argument, unsupported
+from ..kernels import ops
+from .base import Part
+from .linear import Linear
+from .registry import register_part
+from .spec import ParamSpec
+
+
+@register_part("mixer", "attention")
+class Attention(Part):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec.param("hidden_size"))
+        self.heads = int(spec.param("num_heads"))
+        self.kv_heads = int(spec.param("num_kv_heads"))
+        self.head_dim = int(spec.param("head_dim"))
+        self.qk_norm = bool(spec.param("qk_norm", False))
+        self.eps = float(spec.param("qk_norm_eps", 1e-6))
+        self.window = spec.param("window", None)
+        scale = spec.param("scale", None)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(float(self.head_dim))
+        if self.hidden <= 0 or self.heads <= 0 or self.kv_heads <= 0 or self.heads % self.kv_heads or self.head_dim <= 0:
+            raise invalid_argument("invalid attention dimensions")
+        if self.head_dim > 256:
+            raise unsupported(f"head_dim {self.head_dim} exceeds 256, the widest head the kernels take")
+        if self.window is not None and int(self.window) <= 0:
+            raise invalid_argument("an attention window must be positive")
+        name = spec.param("position", None)
+        self.position = env.positions[name] if name is not None else None
+        if self.position is not None and self.position.head_dim != self.head_dim:
+            raise invalid_argument("the rotary encoding was built for another head width")
+        self.q_width = self.heads * self.head_dim
+        self.kv_width = self.kv_heads * self.head_dim
+        self.qkv: Optional[Linear] = None
+        self.out: Optional[Linear] = None
+        self.q_norm = self.k_norm = None
+
+    def parameter_specs(self) -> List[ParamSpec]:
+        specs = [
+            ParamSpec("qkv_proj.weight", (self.q_width + 2 * self.kv_width, self.hidden), sources=(
+                ("q_proj.weight", (self.q_width, self.hidden)),
+                ("k_proj.weight", (self.kv_width, self.hidden)),
+                ("v_proj.weight", (self.kv_width, self.hidden)))),
+            ParamSpec("o_proj.weight", (self.hidden, self.q_width)),
+        ]
+        if self.qk_norm:
+            specs.append(ParamSpec("q_norm.weight", (self.head_dim,), init=("one_plus_normal", 0.1)))
+            specs.append(ParamSpec("k_norm.weight", (self.head_dim,), init=("one_plus_normal", 0.1)))
+        return specs
+
+    def bind(self, tensors) -> None:
+        self.qkv = Linear(tensors["qkv_proj.weight"])
+        self.out = Linear(tensors["o_proj.weight"])
+        if self.qk_norm:
+            self.q_norm, self.k_norm = tensors["q_norm.weight"], tensors["k_norm.weight"]
+            if self.q_norm.dtype != self.k_norm.dtype:
+                self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+
+    def cache_requests(self) -> list:
+        return [KVRequest(self.kv_heads, self.head_dim, int(self.window) if self.window is not None else None)]
+
+    def forward(self, x: torch.Tensor, ctx, views, owns_cache: bool) -> torch.Tensor:
+        view = views[0]
+        plan = ctx.plan
+        qkv = self.qkv.forward(x)
+        position = self.position
+        rotate = dict(cos=position.cos, sin=position.sin, rotary_dim=position.rotary_dim) if position is not None \
+            else dict(cos=None, sin=None, rotary_dim=0)
+        common = dict(heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim)
+        ring = view.ring_pages > 0
+        # A ring that is written before attention would lose keys that the step's
+        # earlier rows still need; it is written afterwards unless the step is one
+        # token per sequence. A full-history cache is written first.
+        store_first = owns_cache and (not ring or plan.is_decode)
+        if not owns_cache and ring and not plan.is_decode:
+            raise unsupported("a layer that reads another layer's windowed cache takes one token per step")
+        ops.rope_store(qkv, q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, tables=ctx.tables, kv_view=view,
+                       store=store_first, **rotate, **common)
+        attended = torch.empty((qkv.shape[0], self.q_width), dtype=qkv.dtype, device=qkv.device)
+        keys_in_step = owns_cache and not plan.is_decode
+        ctx.attention(qkv, attended, scale=self.scale, window=self.window, kv_view=view,
+                      keys_in_step=keys_in_step, **common)
+        if owns_cache and not store_first:
+            ops.rope_store(qkv, q_norm=None, k_norm=None, eps=self.eps, tables=ctx.tables, kv_view=view, store=True,
+                           transform=False, cos=None, sin=None, rotary_dim=0, **common)
+        return self.out.forward(attended)

@@ -1,0 +1,54 @@
+"""Gated feed-forward: y = (act(x Wg^T) * (x Wu^T)) Wd^T.
+
+The reference's GatedFeedForward (src/kidi/layers/gemma4.cpp:164-225): one fused
+projection to [gate | up] (gate = first I columns), the activation on the gate times
+up, then the down projection; no biases. SiLU is g / (1 + exp(-g))
+(src/kidi/runtime/mps/eager_kernels.metal:129-137).
+
+Parameters: hidden_size, intermediate_size, activation ("silu").
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..errors import unsupported
+from ..kernels import ops
+from .base import Part
+from .linear import Linear
+from .registry import register_part
+from .spec import ParamSpec
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedFeedForward(Part):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec.param("hidden_size"))
+        self.inter = int(spec.param("intermediate_size"))
+        activation = spec.param("activation", "silu")
+        if activation != "silu":
+            raise unsupported(f"gated feed-forward activation '{activation}' is not built (silu is)")
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def parameter_specs(self) -> List[ParamSpec]:
+        return [
+            ParamSpec("gate_up_proj.weight", (2 * self.inter, self.hidden), sources=(
+                ("gate_proj.weight", (self.inter, self.hidden)),
+                ("up_proj.weight", (self.inter, self.hidden)))),
+            ParamSpec("down_proj.weight", (self.hidden, self.inter)),
+        ]
+
+    def bind(self, tensors) -> None:
+        self.gate_up = Linear(tensors["gate_up_proj.weight"])
+        self.down = Linear(tensors["down_proj.weight"])
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        from ..kernels import skinny
+        if skinny.fits(x, self.gate_up.weight):
+            gated = skinny.gemm_silu_gate(x, self.gate_up.weight)
+        else:
+            gated = ops.silu_gate(self.gate_up.forward(x))
+        return self.down.forward(gated)

@@ -1,0 +1,38 @@
+"""The tiny configurations the tests run: they differ in every size and option."""
+
+# Two layers, heads 4 over 2 key/value heads, head width 16 (heads * width == hidden), tied
+# embeddings, theta 1e4, eps 1e-6, every layer with full attention.
+TINY_A = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 16, "intermediate_size": 128, "vocab_size": 256, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 128,
+    "attention_bias": False, "eos_token_id": 7,
+}
+
+# Three layers, heads 8 over 2 (group 4), head width 32 (heads * width = 256 != hidden 96),
+# odd intermediate and vocabulary, untied head, theta 1e6, eps 1e-5, the middle layer with a
+# window of 24 tokens (a ring of one page).
+TINY_B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 8, "num_key_value_heads": 2,
+    "head_dim": 32, "intermediate_size": 200, "vocab_size": 389,
+    "rope_parameters": {"rope_theta": 1000000.0, "rope_type": "default"},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 256,
+    "layer_types": ["full_attention", "sliding_attention", "full_attention"], "sliding_window": 24,
+    "eos_token_id": [3, 11],
+}
+
+# Four layers, 6 heads over 3 (group 2), head width 48 (a multiple of 16 that is no power of
+# two), one key/value head per two heads, windows of 70 tokens (a ring of two pages that wraps
+# within 256 positions) on the even layers.
+TINY_C = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu",
+    "num_hidden_layers": 4, "hidden_size": 72, "num_attention_heads": 6, "num_key_value_heads": 3,
+    "head_dim": 48, "intermediate_size": 136, "vocab_size": 301, "rope_theta": 50000.0,
+    "rms_norm_eps": 3e-6, "tie_word_embeddings": False, "max_position_embeddings": 320,
+    "layer_types": ["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+    "sliding_window": 70,
+}
+
+ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
