@@ -1,12 +1,75 @@
-"""The weight-streaming bfloat16 matrix product for few rows (decode)."""
+"""The weight-streaming bfloat16 matrix product for few rows (the decode step).
+
+`fits` says whether a product can take this kernel: bfloat16 on both sides, at most
+`MAX_ROWS` rows, 16-byte aligned rows. `MAX_ROWS` can be lowered or raised with the
+environment variable KIDI_B200_SKINNY_MAX_ROWS (0 switches the kernel off).
+"""
 from __future__ import annotations
+
+import os
+from typing import Optional
 
 import torch
 
+from ..errors import invalid_argument
+from . import ops
+from .ops import _check, _need_cuda, _ptr, _stream, c_int, c_longlong, c_void_p, dtype_code
+
+MAX_ROWS = int(os.environ.get("KIDI_B200_SKINNY_MAX_ROWS", "64"))
+
+_bound = False
+
+
+def _library():
+    global _bound
+    lib = ops.core()
+    if not _bound:
+        lib.kidi_gemm_skinny.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
+                                         c_longlong, c_longlong, c_int, c_int, c_void_p]
+        lib.kidi_gemm_skinny.restype = c_int
+        _bound = True
+    return lib
+
 
 def fits(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    return False
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and weight.dim() == 2
+            and 0 < x.shape[0] <= MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
+            and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0)
 
 
-def gemm(x, weight, out_dtype, out=None):
-    raise NotImplementedError
+def _row_tiles(features: int) -> int:
+    # Two tiles of 16 weight rows per block halve the traffic of the batch operand; one
+    # tile makes twice as many blocks, which narrow matrices need to fill 148 SMs.
+    return 2 if features >= 16384 else 1
+
+
+def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
+         row_tiles: Optional[int] = None) -> torch.Tensor:
+    """y = x @ weight.T for x [M <= 64, K], weight [N, K], both bfloat16."""
+    _need_cuda(x, weight)
+    if not fits(x, weight) or x.shape[1] != weight.shape[1]:
+        raise invalid_argument("gemm_skinny: the operands do not fit this kernel")
+    M, K = x.shape
+    N = weight.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _check(_library().kidi_gemm_skinny(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0),
+                                       weight.stride(0), out.stride(0), 0, row_tiles or _row_tiles(N), _stream()),
+           "gemm_skinny")
+    return out
+
+
+def gemm_silu_gate(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(x @ Wg.T) * (x @ Wu.T) for weight = [Wg; Wu] of shape [2I, K]."""
+    _need_cuda(x, weight)
+    if not fits(x, weight) or x.shape[1] != weight.shape[1] or weight.shape[0] % 2:
+        raise invalid_argument("gemm_silu_gate: the operands do not fit this kernel")
+    M, K = x.shape
+    inter = weight.shape[0] // 2
+    if out is None:
+        out = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
+    _check(_library().kidi_gemm_skinny(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), M, inter, K,
+                                       x.stride(0), weight.stride(0), out.stride(0), 1, 2, _stream()),
+           "gemm_silu_gate")
+    return out
