@@ -1,0 +1,489 @@
+// Causal grouped-query attention in bfloat16 on the tensor cores, compiled for one
+// head width (-DKIDI_HEAD_DIM=..., a multiple of 16 up to 256):
+//
+//  * kidi_attention_prefill: every row of a step (whole prompts, or chunks that
+//    continue a cached prefix) against its sequence's keys. A block owns 64 query
+//    rows of one (sequence, head) and walks the keys in tiles of 64 aligned to
+//    absolute positions; keys of the step's own rows come from the packed qkv rows,
+//    earlier ones from the paged cache.
+//  * kidi_attention_decode: one query row per sequence against the cache only. A
+//    block owns one (sequence, key/value head, split of the key range): the query heads
+//    that share the key/value head are the rows of one tensor-core tile, the four
+//    warps split each 64-key page, and splits are merged by kidi_attention_combine in
+//    split order. Partial results live in a caller-provided workspace.
+//
+// Scores are (q . k) * scale in 32-bit, the softmax (running maximum, exponentials,
+// denominator) is 32-bit, probabilities are rounded to bfloat16 for the product with
+// V, which accumulates in 32-bit. Formulas: src/kidi/layers/qwen3.cpp:53-54,
+// src/kidi/runtime/vulkan/attention.comp:32-101; causal rule
+// src/kidi/model/gemma4.cpp:736-740.
+#include "common.cuh"
+
+#ifndef KIDI_HEAD_DIM
+#error "compile with -DKIDI_HEAD_DIM=<head width>"
+#endif
+
+namespace {
+
+constexpr int D = KIDI_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head width must be a multiple of 16 up to 256");
+constexpr int PITCH = D + 8;            // elements; rows shift by 4 banks, ldmatrix is conflict-free
+constexpr int TILE = 64;                // keys per tile = cache page size
+constexpr int CHUNKS = D / 8;           // 16-byte chunks per row
+constexpr int THREADS = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ unsigned smem_address(const void* pointer) {
+    return (unsigned)__cvta_generic_to_shared(pointer);
+}
+
+__device__ __forceinline__ void copy_async_16(void* shared, const void* global, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0: the destination is filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_address(shared)), "l"(global), "r"(bytes));
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* shared) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_address(shared)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* shared) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_address(shared)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float low, float high) {
+    __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<unsigned*>(&pair);
+}
+
+struct Args {
+    const bf16* q;        // [rows, ldq], head h at h*D
+    long long ldq;
+    const bf16* k_step;   // this step's keys [rows, ldkv], kv head g at g*D (prefill only; may be null)
+    const bf16* v_step;
+    long long ldkv;
+    const bf16* k_cache;  // [pages, kv_heads, 64, D]
+    const bf16* v_cache;
+    CacheGeometry cache;
+    bf16* out;            // [rows, ldo]
+    long long ldo;
+    const int* row_seq;   // [rows]; -1: padding row
+    const int* row_pos;   // [rows]
+    const int* seq_slot;  // [seqs]
+    const int* seq_start; // [seqs] tokens cached before this step
+    const int* seq_len;   // [seqs] tokens this step brings
+    const int* seq_row0;  // [seqs] first packed row
+    int rows, seqs, heads, kv_heads, window;  // window 0: none
+    float scale;
+    // decode only
+    float* partial_out;   // [rows, heads, splits, D]
+    float* partial_stat;  // [rows, heads, splits, 2]  (maximum in log2 units, denominator)
+    int splits;
+};
+
+// Loads one 64 x D tile of keys (or values) for absolute key positions [tile*64, tile*64+64)
+// of a sequence into padded shared memory. Positions >= step_from come from the step's
+// packed rows, earlier ones from the cache; positions > last are zero-filled.
+__device__ __forceinline__ void load_tile(bf16* shared, const bf16* step, long long ld_step, int row0, int step_from,
+                                          const bf16* cache, const CacheGeometry& geometry, int slot, int kv_head,
+                                          int tile, int last) {
+    const int base = tile * TILE;
+    // Cache address of the tile's first row (rows of a page are contiguous).
+    const bf16* page = nullptr;
+    if (cache && base < step_from) page = cache + cache_row_offset(geometry, slot, base, kv_head);
+    for (int chunk = threadIdx.x; chunk < TILE * CHUNKS; chunk += THREADS) {
+        const int r = chunk / CHUNKS, c = chunk - r * CHUNKS;
+        const int u = base + r;
+        const bf16* source = step ? step : cache;
+        bool valid = u <= last;
+        if (valid) {
+            if (u >= step_from) source = step + (long long)(row0 + u - step_from) * ld_step + (long long)kv_head * D + c * 8;
+            else source = page + (long long)r * D + c * 8;
+        }
+        copy_async_16(shared + r * PITCH + c * 8, source, valid);
+    }
+}
+
+// Online-softmax update of one warp's 16 x (NT*8) score tile `s` (already in log2
+// units and masked with -inf) followed by P*V. Rows g and g+8 of the tile.
+template <int NT>
+__device__ __forceinline__ void softmax_and_weighted_sum(float (&s)[NT][4], float (&best)[2], float (&denom)[2],
+                                                        float (&o)[D / 8][4], const bf16* v_tile, int first_key,
+                                                        int lane) {
+    float top[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        top[0] = fmaxf(top[0], fmaxf(s[j][0], s[j][1]));
+        top[1] = fmaxf(top[1], fmaxf(s[j][2], s[j][3]));
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        top[i] = fmaxf(top[i], __shfl_xor_sync(0xffffffffu, top[i], 1));
+        top[i] = fmaxf(top[i], __shfl_xor_sync(0xffffffffu, top[i], 2));
+    }
+    float keep[2], use[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float next = fmaxf(best[i], top[i]);
+        use[i] = next == -INFINITY ? 0.f : next;  // a row that has seen no key yet
+        keep[i] = exp2f(best[i] - use[i]);
+        best[i] = next;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        s[j][0] = exp2f(s[j][0] - use[0]);
+        s[j][1] = exp2f(s[j][1] - use[0]);
+        s[j][2] = exp2f(s[j][2] - use[1]);
+        s[j][3] = exp2f(s[j][3] - use[1]);
+        sum[0] += s[j][0] + s[j][1];
+        sum[1] += s[j][2] + s[j][3];
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+        denom[i] = denom[i] * keep[i] + sum[i];
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        o[n][0] *= keep[0];
+        o[n][1] *= keep[0];
+        o[n][2] *= keep[1];
+        o[n][3] *= keep[1];
+    }
+    // P (bf16) times V: 16 keys per k-step = two score tiles.
+    const int matrix = lane >> 3, within = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        unsigned p[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                         pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+        const int key = first_key + kk * 16 + within + (matrix & 1) * 8;
+#pragma unroll
+        for (int n = 0; n < D / 16; ++n) {
+            unsigned v[4];
+            ldmatrix_x4_trans(v, v_tile + key * PITCH + n * 16 + (matrix >> 1) * 8);
+            mma_bf16(o[2 * n], p, v[0], v[1]);
+            mma_bf16(o[2 * n + 1], p, v[2], v[3]);
+        }
+    }
+}
+
+// Scores of one warp: 16 query rows (A from q_tile rows [q_row, q_row+16)) against
+// NT*8 keys starting at `first_key` of k_tile, times scale_log2.
+template <int NT>
+__device__ __forceinline__ void scores(float (&s)[NT][4], const bf16* q_tile, int q_row, const bf16* k_tile,
+                                       int first_key, float scale_log2, int lane) {
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
+    const int matrix = lane >> 3, within = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        unsigned a[4];
+        ldmatrix_x4(a, q_tile + (q_row + within + (matrix & 1) * 8) * PITCH + kk * 16 + (matrix >> 1) * 8);
+#pragma unroll
+        for (int jj = 0; jj < NT / 2; ++jj) {
+            unsigned b[4];
+            ldmatrix_x4(b, k_tile + (first_key + jj * 16 + within + (matrix >> 1) * 8) * PITCH + kk * 16 + (matrix & 1) * 8);
+            mma_bf16(s[2 * jj], a, b[0], b[1]);
+            mma_bf16(s[2 * jj + 1], a, b[2], b[3]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[j][i] *= scale_log2;
+}
+
+// ------------------------------------------------------------------- prefill
+__global__ void __launch_bounds__(THREADS) attention_prefill_kernel(Args a) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    bf16* q_tile = reinterpret_cast<bf16*>(raw);            // [64][PITCH]
+    bf16* k_tiles = q_tile + TILE * PITCH;                  // [2][64][PITCH]
+    bf16* v_tiles = k_tiles + 2 * TILE * PITCH;             // [2][64][PITCH]
+    const int seq = blockIdx.y, head = blockIdx.z;
+    const int q0 = blockIdx.x * TILE;
+    const int count = a.seq_len[seq];
+    if (q0 >= count) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int start = a.seq_start[seq], row0 = a.seq_row0[seq], slot = a.seq_slot[seq];
+    const int kv_head = head / (a.heads / a.kv_heads);
+    const int q_rows = min(TILE, count - q0);
+    const int last = start + count - 1;                     // last key position that exists
+    const int step_from = a.k_step ? start : 0x7fffffff;
+    const int high = start + q0 + q_rows - 1;               // largest query position of the block
+    const int low = a.window > 0 ? max(0, start + q0 - a.window + 1) : 0;
+    const int tile_low = low / TILE, tile_high = high / TILE;
+
+    for (int chunk = threadIdx.x; chunk < TILE * CHUNKS; chunk += THREADS) {
+        const int r = chunk / CHUNKS, c = chunk - r * CHUNKS;
+        const bool valid = r < q_rows;
+        const bf16* source = a.q + (long long)(row0 + q0 + (valid ? r : 0)) * a.ldq + (long long)head * D + c * 8;
+        copy_async_16(q_tile + r * PITCH + c * 8, source, valid);
+    }
+    load_tile(k_tiles, a.k_step, a.ldkv, row0, step_from, a.k_cache, a.cache, slot, kv_head, tile_low, last);
+    load_tile(v_tiles, a.v_step, a.ldkv, row0, step_from, a.v_cache, a.cache, slot, kv_head, tile_low, last);
+    copy_async_commit();
+
+    float best[2] = {-INFINITY, -INFINITY}, denom[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+    const float scale_log2 = a.scale * LOG2E;
+    const int position0 = start + q0 + warp * 16 + g;       // query position of accumulator rows 0,1 (and +8 for 2,3)
+
+    for (int tile = tile_low; tile <= tile_high; ++tile) {
+        const int buffer = (tile - tile_low) & 1;
+        if (tile < tile_high) {
+            load_tile(k_tiles + (buffer ^ 1) * TILE * PITCH, a.k_step, a.ldkv, row0, step_from, a.k_cache, a.cache,
+                      slot, kv_head, tile + 1, last);
+            load_tile(v_tiles + (buffer ^ 1) * TILE * PITCH, a.v_step, a.ldkv, row0, step_from, a.v_cache, a.cache,
+                      slot, kv_head, tile + 1, last);
+            copy_async_commit();
+            copy_async_wait<1>();
+        } else {
+            copy_async_wait<0>();
+        }
+        __syncthreads();
+        // Warps whose 16 query rows do not exist, or lie wholly before this tile, have nothing to do.
+        const bool active = warp * 16 < q_rows && start + q0 + warp * 16 + 15 >= tile * TILE;
+        if (active) {
+            float s[8][4];
+            scores<8>(s, q_tile, warp * 16, k_tiles + buffer * TILE * PITCH, 0, scale_log2, lane);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int u = tile * TILE + j * 8 + 2 * t + (i & 1);
+                    const int p = position0 + (i >> 1) * 8;
+                    const bool visible = u <= p && (a.window <= 0 || u > p - a.window);
+                    if (!visible) s[j][i] = -INFINITY;
+                }
+            softmax_and_weighted_sum<8>(s, best, denom, o, v_tiles + buffer * TILE * PITCH, 0, lane);
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + g + half * 8;
+        if (r >= q_rows) continue;
+        const float inverse = 1.0f / denom[half];
+        bf16* out = a.out + (long long)(row0 + q0 + r) * a.ldo + (long long)head * D;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            const unsigned pair = pack_bf16(o[n][half * 2] * inverse, o[n][half * 2 + 1] * inverse);
+            *reinterpret_cast<unsigned*>(out + n * 8 + 2 * t) = pair;
+        }
+    }
+}
+
+// -------------------------------------------------------------------- decode
+// grid (splits, kv_heads, rows). The `group` query heads of a key/value head are rows
+// 0..group-1 of a 16-row tile (group <= 16); warp w takes keys 16w..16w+15 of each page.
+__global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    bf16* q_tile = reinterpret_cast<bf16*>(raw);            // [16][PITCH]
+    bf16* k_tiles = q_tile + 16 * PITCH;                    // [2][64][PITCH]
+    bf16* v_tiles = k_tiles + 2 * TILE * PITCH;             // [2][64][PITCH]
+    const int split = blockIdx.x, kv_head = blockIdx.y, row = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = a.heads / a.kv_heads;
+    const int seq = a.row_seq[row];
+    const int head0 = kv_head * group;
+    float* merged_out = a.partial_out;   // set below when splits > 1
+    float best[2] = {-INFINITY, -INFINITY}, denom[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+
+    int tiles = 0, tile_first = 0, position = 0, low = 0, slot = 0;
+    if (seq >= 0) {
+        position = a.row_pos[row];
+        slot = a.seq_slot[seq];
+        low = a.window > 0 ? max(0, position - a.window + 1) : 0;
+        const int tile_low = low / TILE, tile_high = position / TILE;
+        const int all = tile_high - tile_low + 1;
+        const int per_split = (all + a.splits - 1) / a.splits;
+        tile_first = tile_low + split * per_split;
+        tiles = max(0, min(per_split, tile_high + 1 - tile_first));
+    }
+    if (tiles > 0) {
+        for (int chunk = threadIdx.x; chunk < 16 * CHUNKS; chunk += THREADS) {
+            const int r = chunk / CHUNKS, c = chunk - r * CHUNKS;
+            const bool valid = r < group;
+            const bf16* source = a.q + (long long)row * a.ldq + (long long)(head0 + (valid ? r : 0)) * D + c * 8;
+            copy_async_16(q_tile + r * PITCH + c * 8, source, valid);
+        }
+        load_tile(k_tiles, nullptr, 0, 0, 0x7fffffff, a.k_cache, a.cache, slot, kv_head, tile_first, position);
+        load_tile(v_tiles, nullptr, 0, 0, 0x7fffffff, a.v_cache, a.cache, slot, kv_head, tile_first, position);
+        copy_async_commit();
+        const float scale_log2 = a.scale * LOG2E;
+        for (int index = 0; index < tiles; ++index) {
+            const int tile = tile_first + index, buffer = index & 1;
+            if (index + 1 < tiles) {
+                load_tile(k_tiles + (buffer ^ 1) * TILE * PITCH, nullptr, 0, 0, 0x7fffffff, a.k_cache, a.cache, slot,
+                          kv_head, tile + 1, position);
+                load_tile(v_tiles + (buffer ^ 1) * TILE * PITCH, nullptr, 0, 0, 0x7fffffff, a.v_cache, a.cache, slot,
+                          kv_head, tile + 1, position);
+                copy_async_commit();
+                copy_async_wait<1>();
+            } else {
+                copy_async_wait<0>();
+            }
+            __syncthreads();
+            const int first_key = warp * 16;
+            if (tile * TILE + first_key <= position && tile * TILE + first_key + 15 >= low) {
+                float s[2][4];
+                scores<2>(s, q_tile, 0, k_tiles + buffer * TILE * PITCH, first_key, scale_log2, lane);
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int u = tile * TILE + first_key + j * 8 + 2 * t + (i & 1);
+                        if (u > position || u < low) s[j][i] = -INFINITY;
+                    }
+                softmax_and_weighted_sum<2>(s, best, denom, o, v_tiles + buffer * TILE * PITCH, first_key, lane);
+            }
+            __syncthreads();
+        }
+    }
+
+    // Merge the four warps in warp order through shared memory (the tiles are free now).
+    float* merge_out = reinterpret_cast<float*>(k_tiles);                // [4][16][D]
+    float* merge_stat = merge_out + 4 * 16 * D;                          // [4][16][2]
+    __syncthreads();
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = g + half * 8;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            merge_out[(warp * 16 + r) * D + n * 8 + 2 * t] = o[n][half * 2];
+            merge_out[(warp * 16 + r) * D + n * 8 + 2 * t + 1] = o[n][half * 2 + 1];
+        }
+        if (t == 0) {
+            merge_stat[(warp * 16 + r) * 2] = best[half];
+            merge_stat[(warp * 16 + r) * 2 + 1] = denom[half];
+        }
+    }
+    __syncthreads();
+    for (int item = threadIdx.x; item < group * D; item += THREADS) {
+        const int r = item / D, c = item - r * D;
+        float top = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) top = fmaxf(top, merge_stat[(w * 16 + r) * 2]);
+        float total = 0.f, value = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float m = merge_stat[(w * 16 + r) * 2];
+            const float factor = m == -INFINITY ? 0.f : exp2f(m - top);
+            total += merge_stat[(w * 16 + r) * 2 + 1] * factor;
+            value += merge_out[(w * 16 + r) * D + c] * factor;
+        }
+        const int head = head0 + r;
+        if (a.splits == 1) {
+            a.out[(long long)row * a.ldo + (long long)head * D + c] =
+                from_float<bf16>(total > 0.f ? value / total : 0.f);
+        } else {
+            const long long where = ((long long)row * a.heads + head) * a.splits + split;
+            merged_out[where * D + c] = value;
+            if (c == 0) {
+                a.partial_stat[where * 2] = top;
+                a.partial_stat[where * 2 + 1] = total;
+            }
+        }
+    }
+}
+
+// grid (heads, rows): merges the splits of one (row, head) in split order.
+__global__ void attention_combine_kernel(Args a) {
+    const int head = blockIdx.x, row = blockIdx.y;
+    const long long where = ((long long)row * a.heads + head) * a.splits;
+    float top = -INFINITY;
+    for (int s = 0; s < a.splits; ++s) top = fmaxf(top, a.partial_stat[(where + s) * 2]);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float total = 0.f, value = 0.f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float m = a.partial_stat[(where + s) * 2];
+            const float factor = m == -INFINITY ? 0.f : exp2f(m - top);
+            total += a.partial_stat[(where + s) * 2 + 1] * factor;
+            value += a.partial_out[(where + s) * D + c] * factor;
+        }
+        a.out[(long long)row * a.ldo + (long long)head * D + c] = from_float<bf16>(total > 0.f ? value / total : 0.f);
+    }
+}
+
+constexpr size_t PREFILL_SHARED = (size_t)(TILE + 4 * TILE) * PITCH * sizeof(bf16);
+constexpr size_t DECODE_TILES = (size_t)(16 + 4 * TILE) * PITCH * sizeof(bf16);
+constexpr size_t DECODE_MERGE = (size_t)16 * PITCH * sizeof(bf16) + (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
+constexpr size_t DECODE_SHARED = DECODE_TILES > DECODE_MERGE ? DECODE_TILES : DECODE_MERGE;
+
+bool aligned(const Args& a) {
+    return !((uintptr_t)a.q & 15) && !((uintptr_t)a.k_step & 15) && !((uintptr_t)a.v_step & 15) &&
+           !((uintptr_t)a.k_cache & 15) && !((uintptr_t)a.v_cache & 15) && !((uintptr_t)a.out & 3) && !(a.ldq & 7) &&
+           !(a.ldkv & 7) && !(a.ldo & 1);
+}
+}  // namespace
+
+KIDI_API int kidi_attention_head_dim() { return D; }
+
+// max_new: the longest seq_len of the step (sizes the grid).
+KIDI_API int kidi_attention_prefill(const Args* args, int max_new, cudaStream_t stream) {
+    const Args& a = *args;
+    if (a.rows <= 0 || a.seqs <= 0 || max_new <= 0) return 0;
+    if (a.cache.head_dim != D || a.heads % a.kv_heads || a.heads > 65535 || a.seqs > 65535 || !aligned(a) ||
+        (a.cache.table && a.cache.page_shift != 6))
+        return KIDI_REFUSED_SIZE;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)PREFILL_SHARED);
+        if (status != cudaSuccess) return (int)status;
+        configured = true;
+    }
+    dim3 grid((max_new + TILE - 1) / TILE, a.seqs, a.heads);
+    attention_prefill_kernel<<<grid, THREADS, PREFILL_SHARED, stream>>>(a);
+    return kidi_launch_status();
+}
+
+// One query row per sequence; every key comes from the cache. With splits > 1 the
+// workspace pointers must hold rows*heads*splits*(D + 2) floats.
+KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
+    const Args& a = *args;
+    if (a.rows <= 0) return 0;
+    const int group = a.kv_heads > 0 ? a.heads / a.kv_heads : 0;
+    if (a.cache.head_dim != D || a.heads % a.kv_heads || group > 16 || a.kv_heads > 65535 || a.rows > 65535 ||
+        !aligned(a) || a.cache.page_shift != 6 || a.splits < 1 || (a.splits > 1 && (!a.partial_out || !a.partial_stat)))
+        return KIDI_REFUSED_SIZE;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)DECODE_SHARED);
+        if (status != cudaSuccess) return (int)status;
+        configured = true;
+    }
+    dim3 grid(a.splits, a.kv_heads, a.rows);
+    attention_decode_kernel<<<grid, THREADS, DECODE_SHARED, stream>>>(a);
+    int status = kidi_launch_status();
+    if (status || a.splits == 1) return status;
+    dim3 combine(a.heads, a.rows);
+    attention_combine_kernel<<<combine, D >= 128 ? 128 : 64, 0, stream>>>(a);
+    return kidi_launch_status();
+}

@@ -44,11 +44,21 @@ class StepContext:
     """What parts see of a step."""
 
     def __init__(self, plan: StepPlan, tables: DeviceTables, cache: SequenceCache, dtype: torch.dtype,
-                 device: torch.device):
+                 device: torch.device, workspaces: Optional[Dict[str, torch.Tensor]] = None):
         self.plan, self.tables, self.cache, self.dtype, self.device = plan, tables, cache, dtype, device
+        self._workspaces = workspaces if workspaces is not None else {}
 
     def attention(self, qkv, out, **arguments) -> None:
         attention_kernels.run(self, qkv, out, **arguments)
+
+    def workspace(self, name: str, count: int) -> torch.Tensor:
+        """Scratch memory of at least `count` float32 elements that kernels of one
+        step may use one after another (it is kept between steps and grows on demand)."""
+        held = self._workspaces.get(name)
+        if held is None or held.numel() < count:
+            held = torch.empty(max(count, 1), dtype=torch.float32, device=self.device)
+            self._workspaces[name] = held
+        return held
 
 
 class Engine:
@@ -68,7 +78,7 @@ class Engine:
         self._staging = [None, None]      # pinned host buffers, used in turn
         self._staging_done = [None, None]  # events: the copy out of the buffer has finished
         self._turn = 0
-        self._tables_buffer: Optional[torch.Tensor] = None
+        self._workspaces: Dict[str, torch.Tensor] = {}
 
     # ---------------------------------------------------------------- loading
     @classmethod
@@ -142,7 +152,7 @@ class Engine:
             growth = [(slot, start + int(count)) for slot, start, count in zip(batch.slots, starts, plan.seq_len)]
             self.cache.reserve(growth)
             self.cache.flush_tables()
-            ctx = StepContext(plan, self._upload(plan), self.cache, self.dtype, self.device)
+            ctx = StepContext(plan, self._upload(plan), self.cache, self.dtype, self.device, self._workspaces)
             logits = self.model.forward(ctx)
             self.cache.commit(growth)
             return logits

@@ -1,14 +1,100 @@
-"""Chooses the attention kernel for a step.
+"""Chooses and launches the attention kernel for a step.
 
 The generic kernel takes every element type, head width up to 256 and any number of
-heads, for prompts and for single tokens, and is the only one the 32-bit engine uses.
-The bfloat16 engine uses the tensor-core kernels where the shape fits them.
+heads, for prompts and for single tokens; it is the only one the 32-bit engine uses.
+The bfloat16 engine uses the tensor-core kernels, which are compiled for the head
+width of the loaded model at the first call: a prefill kernel for steps that bring
+several tokens per sequence and a split-key decode kernel for steps of one token per
+sequence. Setting KIDI_B200_GENERIC_ATTENTION=1 forces the generic kernel.
 """
 from __future__ import annotations
 
+import ctypes
+import os
+from typing import Dict
+
+import torch
+
+from ..csrc.build import load_library
 from . import ops
+from .ops import CacheGeometry, _check, c_float, c_int, c_longlong, c_void_p, cache_geometry
+
+FORCE_GENERIC = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1"
+
+
+class FastAttentionArgs(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("ldq", c_longlong), ("k_step", c_void_p), ("v_step", c_void_p),
+                ("ldkv", c_longlong), ("k_cache", c_void_p), ("v_cache", c_void_p), ("cache", CacheGeometry),
+                ("out", c_void_p), ("ldo", c_longlong), ("row_seq", c_void_p), ("row_pos", c_void_p),
+                ("seq_slot", c_void_p), ("seq_start", c_void_p), ("seq_len", c_void_p), ("seq_row0", c_void_p),
+                ("rows", c_int), ("seqs", c_int), ("heads", c_int), ("kv_heads", c_int), ("window", c_int),
+                ("scale", c_float), ("partial_out", c_void_p), ("partial_stat", c_void_p), ("splits", c_int)]
+
+
+_libraries: Dict[int, ctypes.CDLL] = {}
+_sm_count: Dict[int, int] = {}
+
+
+def library(head_dim: int) -> ctypes.CDLL:
+    """The tensor-core attention kernels compiled for one head width."""
+    lib = _libraries.get(head_dim)
+    if lib is None:
+        lib = load_library(f"attention_d{head_dim}", ("attention_bf16.cu",), {"KIDI_HEAD_DIM": head_dim})
+        lib.kidi_attention_prefill.argtypes = [c_void_p, c_int, c_void_p]
+        lib.kidi_attention_decode.argtypes = [c_void_p, c_void_p]
+        lib.kidi_attention_prefill.restype = lib.kidi_attention_decode.restype = c_int
+        _libraries[head_dim] = lib
+    return lib
+
+
+def fast_fits(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, decode: bool) -> bool:
+    if FORCE_GENERIC or dtype != torch.bfloat16 or head_dim % 16 or head_dim > 256 or heads % kv_heads:
+        return False
+    return not decode or heads // kv_heads <= 16
+
+
+def sm_count(device: torch.device) -> int:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _sm_count:
+        _sm_count[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_count[index]
+
+
+def decode_splits(rows: int, kv_heads: int, longest: int, device: torch.device) -> int:
+    """How many blocks share a sequence's keys: enough to give every SM two blocks,
+    at most one per 64-key page."""
+    pages = max(1, -(-longest // 64))
+    wanted = -(-2 * sm_count(device) // max(1, rows * kv_heads))
+    return max(1, min(pages, wanted))
 
 
 def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step) -> None:
-    ops.attention_generic(qkv, out, heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window,
-                          tables=ctx.tables, kv_view=kv_view, keys_in_step=keys_in_step)
+    plan, tables = ctx.plan, ctx.tables
+    decode = plan.is_decode and not keys_in_step
+    if not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode) or (kv_view is not None and kv_view.page_size != 64):
+        ops.attention_generic(qkv, out, heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale,
+                              window=window, tables=tables, kv_view=kv_view, keys_in_step=keys_in_step)
+        return
+    item = qkv.element_size()
+    args = FastAttentionArgs(
+        qkv.data_ptr(), qkv.stride(0),
+        qkv.data_ptr() + heads * head_dim * item if keys_in_step else 0,
+        qkv.data_ptr() + (heads + kv_heads) * head_dim * item if keys_in_step else 0, qkv.stride(0),
+        kv_view.keys.data_ptr() if kv_view is not None else 0, kv_view.values.data_ptr() if kv_view is not None else 0,
+        cache_geometry(kv_view, kv_heads, head_dim), out.data_ptr(), out.stride(0),
+        tables.row_seq.data_ptr(), tables.row_pos.data_ptr(), tables.seq_slot.data_ptr(), tables.seq_start.data_ptr(),
+        tables.seq_len.data_ptr(), tables.seq_row0.data_ptr(), qkv.shape[0], plan.n_seqs, heads, kv_heads,
+        int(window or 0), float(scale), 0, 0, 1)
+    lib = library(head_dim)
+    stream = ops._stream()
+    if decode:
+        longest = min(plan.max_total, int(window)) + 64 if window else plan.max_total
+        splits = getattr(ctx, "decode_splits", None) or decode_splits(qkv.shape[0], kv_heads, longest, qkv.device)
+        if splits > 1:
+            workspace = ctx.workspace("attention_partial", qkv.shape[0] * heads * splits * (head_dim + 2))
+            args.partial_out = workspace.data_ptr()
+            args.partial_stat = workspace.data_ptr() + qkv.shape[0] * heads * splits * head_dim * 4
+        args.splits = splits
+        _check(lib.kidi_attention_decode(ctypes.byref(args), stream), "attention_decode")
+    else:
+        _check(lib.kidi_attention_prefill(ctypes.byref(args), plan.max_new, stream), "attention_prefill")

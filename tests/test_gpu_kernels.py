@@ -225,9 +225,35 @@ def reference_attention(q, keys, values, positions, window, scale):
     return out.reshape(rows, heads * width)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("geometry", [(6, 2, 48, None), (4, 4, 128, None), (8, 1, 16, 37), (2, 1, 80, 100)])
-def test_attention_over_cache(dtype, geometry):
+class FakeContext:
+    """What the attention launcher needs of a step."""
+
+    def __init__(self, plan, tables, splits=None):
+        self.plan, self.tables = plan, tables
+        self.decode_splits = splits
+        self._held = {}
+
+    def workspace(self, name, count):
+        if name not in self._held or self._held[name].numel() < count:
+            self._held[name] = torch.empty(count, dtype=torch.float32, device=DEVICE)
+        return self._held[name]
+
+
+def launch_attention(kind, plan, tables, qkv, out, splits=None, **arguments):
+    from kidi_b200.kernels import attention, ops
+    if kind == "generic":
+        ops.attention_generic(qkv, out, tables=tables, **arguments)
+    else:
+        assert attention.fast_fits(qkv.dtype, arguments["heads"], arguments["kv_heads"], arguments["head_dim"],
+                                   plan.is_decode and not arguments["keys_in_step"])
+        attention.run(FakeContext(plan, tables, splits), qkv, out, **arguments)
+
+
+@pytest.mark.parametrize("kind,dtype", [("generic", torch.float32), ("generic", torch.bfloat16),
+                                        ("tensor_core", torch.bfloat16)])
+@pytest.mark.parametrize("geometry", [(6, 2, 48, None), (4, 4, 128, None), (8, 1, 16, 37), (2, 1, 80, 100),
+                                      (16, 2, 64, None), (3, 1, 256, 70)])
+def test_attention_over_cache(kind, dtype, geometry):
     """Prompts of unequal length and single tokens against a cache filled by earlier
     steps, with one far key made to dominate."""
     from kidi_b200.kernels import ops
@@ -283,15 +309,71 @@ def test_attention_over_cache(dtype, geometry):
                            eps=0.0, cos=None, sin=None, rotary_dim=0, tables=tables, kv_view=view, store=True,
                            transform=False)
         out = torch.empty(plan.n_rows, heads * head_dim, dtype=dtype, device=DEVICE)
-        ops.attention_generic(device_qkv, out, heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale,
-                              window=window, tables=tables, kv_view=view, keys_in_step=keys_in_step)
+        launch_attention(kind, plan, tables, device_qkv, out, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                         scale=scale, window=window, kv_view=view, keys_in_step=keys_in_step)
         for index in range(len(slots)):
             row0, new, start = int(plan.seq_row0[index]), news[index], starts[index]
             keys, values = history[index]
             q = qkv[row0:row0 + new, :heads * head_dim].float().reshape(new, heads, head_dim)
             expected = reference_attention(q, keys, values, plan.row_pos[row0:row0 + new], window, scale)
             close(out[row0:row0 + new], expected, tolerance,
-                  f"sequence {index} (start {start}, new {new}, in step {keys_in_step})")
+                  f"{kind}: sequence {index} (start {start}, new {new}, in step {keys_in_step})")
+
+
+@pytest.mark.parametrize("kind,dtype", [("generic", torch.float32), ("tensor_core", torch.bfloat16)])
+@pytest.mark.parametrize("geometry", [(8, 2, 128, None), (6, 6, 48, None), (16, 1, 32, 90), (4, 2, 64, 64)])
+@pytest.mark.parametrize("splits", [1, 3, 40])
+def test_attention_decode(kind, dtype, geometry, splits):
+    """One token per sequence against caches of very different lengths, with the key
+    range split over several blocks; the far key at position 7 must be found."""
+    from kidi_b200.engine.plan import StepBatch, build_plan
+    from kidi_b200.kernels import ops
+    if kind == "generic" and splits > 1:
+        pytest.skip("the generic kernel does not split keys")
+    heads, kv_heads, head_dim, window = geometry
+    scale = 1.0 / math.sqrt(head_dim)
+    starts = [0, 63, 64, 300, 1000, 127]
+    news = [1] * len(starts)
+    cache, slots, plan, tables = make_cache_and_tables(starts, news, kv_heads, head_dim, window, dtype,
+                                                       max_tokens=8192)
+    view = cache.views(0)[0]
+    generator = torch.Generator().manual_seed(head_dim * 7 + heads)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = torch.zeros(len(starts), width)
+    history = {}
+    for index, (slot, start) in enumerate(zip(slots, starts)):
+        total = start + 1
+        keys = torch.randn(total, kv_heads, head_dim, generator=generator)
+        values = torch.randn(total, kv_heads, head_dim, generator=generator)
+        q = torch.randn(1, heads, head_dim, generator=generator)
+        if total > 150:
+            keys[7] *= 0.0
+            keys[7, :, 0] = 30.0
+            q[:, :, 0] = 4.0
+        history[index] = (keys.to(dtype).float(), values.to(dtype).float())
+        writer = build_plan(StepBatch([slot], [[0] * total]), [0], vocab_size=10)
+        writer_tables = Tables()
+        for name in writer.FIELDS:
+            setattr(writer_tables, name, torch.from_numpy(getattr(writer, name)).to(DEVICE))
+        packed = torch.zeros(total, width)
+        packed[:, heads * head_dim:(heads + kv_heads) * head_dim] = keys.reshape(total, -1)
+        packed[:, (heads + kv_heads) * head_dim:] = values.reshape(total, -1)
+        ops.rope_store(packed.to(dtype).to(DEVICE), heads=heads, kv_heads=kv_heads, head_dim=head_dim, q_norm=None,
+                       k_norm=None, eps=0.0, cos=None, sin=None, rotary_dim=0, tables=writer_tables, kv_view=view,
+                       store=True, transform=False)
+        qkv[index, :heads * head_dim] = q.reshape(-1)
+    qkv = qkv.to(dtype)
+    out = torch.empty(len(starts), heads * head_dim, dtype=dtype, device=DEVICE)
+    launch_attention(kind, plan, tables, qkv.to(DEVICE), out, splits=splits, heads=heads, kv_heads=kv_heads,
+                     head_dim=head_dim, scale=scale, window=window, kv_view=view, keys_in_step=False)
+    # 32-bit: a thousand keys are summed into one accumulator, each addition rounding at
+    # 2^-24 of the running value; the rounding adds like a random walk.
+    tolerance = 1e-5 if dtype == torch.float32 else 1e-2
+    for index, start in enumerate(starts):
+        keys, values = history[index]
+        q = qkv[index:index + 1, :heads * head_dim].float().reshape(1, heads, head_dim)
+        expected = reference_attention(q, keys, values, [start], window, scale)
+        close(out[index:index + 1], expected, tolerance, f"{kind}: sequence of {start + 1} tokens, {splits} splits")
 
 
 def test_window_edge():
