@@ -103,6 +103,30 @@ KIDI_API int kidi_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     return KIDI_REFUSED_DTYPE;
 }
 
+// ------------------------------------------------------- advancing a decode step
+// After a decode step whose tokens were selected on the device: every live row takes
+// its selected token as the next input and moves one position on. Rows whose
+// row_seq is negative are padding and stay as they are.
+__global__ void advance_decode_kernel(int* __restrict__ tokens, const int* __restrict__ selected,
+                                      const int* __restrict__ row_seq, int* __restrict__ row_pos,
+                                      int* __restrict__ seq_start, int* __restrict__ steps, int rows, int vocab) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows || row_seq[r] < 0) return;
+    const int token = selected[r];
+    tokens[r] = token >= 0 && token < vocab ? token : 0;
+    row_pos[r] += 1;
+    seq_start[row_seq[r]] += 1;
+    steps[r] += 1;
+}
+
+KIDI_API int kidi_advance_decode(int* tokens, const int* selected, const int* row_seq, int* row_pos, int* seq_start,
+                                 int* steps, int rows, int vocab, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    advance_decode_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(tokens, selected, row_seq, row_pos, seq_start, steps,
+                                                                  rows, vocab);
+    return kidi_launch_status();
+}
+
 // ------------------------------------------------------------------ SiLU gate
 // gate_up [rows, 2*inter] (gate = first inter columns, up = last inter) -> out [rows, inter]
 template <typename T>

@@ -1,0 +1,174 @@
+"""The decode step of a batch, captured once as a CUDA graph and replayed.
+
+A decode step launches a few hundred small kernels; launching them one by one from
+the host costs as much as running them. The reference captures its recorded decode
+step into a `cudaGraph` and replays it, with pointer-stable tables for what changes
+between steps (src/kidi/runtime/cuda/operators.cpp:202-277,292,438-471). Here a
+`DecodeSession` owns static device buffers for a batch of up to `capacity` rows: the
+step's integer tables, the sampling parameters and the selected tokens. The captured
+graph runs the model's ordinary forward pass over those buffers, selects a token per
+row on the device, and advances tokens and positions for the next step. Between
+replays the host only rewrites the buffers (one copy) when the set of live sequences
+changes, and reads the selected tokens back.
+
+Rows beyond the live sequences are padding: their `row_seq` is -1, so they write
+nothing to the cache and attend to nothing; what the other kernels compute for them is
+never read.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..errors import invalid_argument
+from ..kernels import attention as attention_kernels
+from ..kernels import ops
+from .plan import StepPlan
+
+
+class DecodeSession:
+    FIELDS = ("tokens", "row_seq", "row_pos", "seq_slot", "seq_start", "seq_len", "seq_row0", "want_rows", "steps")
+
+    def __init__(self, engine, capacity: int, sampler, *, longest: Optional[int] = None):
+        from .engine import DeviceTables, StepContext
+        self.engine = engine
+        self.capacity = capacity
+        self.sampler = sampler
+        device = engine.device
+        padded = -(-capacity // 4) * 4
+        self._padded = padded
+        # One int32 buffer: the FIELDS, then temperature (float32 bits), then keys (int64 as two words).
+        words = padded * (len(self.FIELDS) + 1 + 2)
+        self.buffer = torch.zeros(words, dtype=torch.int32, device=device)
+        self.staging = torch.zeros(words, dtype=torch.int32).pin_memory()
+        self._host = self.staging.numpy()
+        offsets = {name: (index * padded, capacity) for index, name in enumerate(self.FIELDS)}
+        self.tables = DeviceTables(self.buffer, offsets)
+        base = len(self.FIELDS) * padded
+        self.temperature = self.buffer[base:base + capacity].view(torch.float32)
+        self.keys = self.buffer[base + padded:base + padded + 2 * capacity].view(torch.int64)
+        self._offsets = offsets
+        self._temperature_at = base
+        self._keys_at = base + padded
+        self.selected = torch.zeros(capacity, dtype=torch.int32, device=device)
+        self.selected_host = torch.zeros(capacity, dtype=torch.int32).pin_memory()
+        self.logits: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.live = 0
+        rows = np.arange(capacity, dtype=np.int32)
+        self._plan = StepPlan(
+            n_rows=capacity, n_seqs=capacity, n_want=capacity, max_new=1,
+            max_total=longest or engine.spec.max_positions, is_decode=True,
+            tokens=rows * 0, row_seq=rows, row_pos=rows * 0, seq_slot=rows * 0, seq_start=rows * 0,
+            seq_len=rows * 0 + 1, seq_row0=rows, want_rows=rows)
+        self._context = StepContext(self._plan, self.tables, engine.cache, engine.dtype, device, engine._workspaces)
+        heads = _widest_decode(engine)
+        if heads is not None:
+            # The number of key splits is a launch dimension: it is fixed when the graph is
+            # captured, from the longest sequence this session may come to hold.
+            self._context.decode_splits = attention_kernels.decode_splits(
+                capacity, heads, self._plan.max_total, device)
+        self._stream = torch.cuda.Stream(device=device)
+
+    # ------------------------------------------------------------------ set-up
+    def load(self, slots: Sequence[int], tokens: Sequence[int], temperature: Sequence[float], keys: Sequence[int],
+             steps: Sequence[int]) -> None:
+        """Sets the live sequences: row r continues the sequence in `slots[r]` with the
+        input token `tokens[r]` at the position the cache says it has reached."""
+        live = len(slots)
+        if live < 1 or live > self.capacity:
+            raise invalid_argument(f"a decode session of {self.capacity} rows cannot hold {live} sequences")
+        if len(set(slots)) != live:
+            raise invalid_argument("a step names a cache slot twice")
+        cache = self.engine.cache
+        starts = [cache.length(slot) for slot in slots]
+        host, padded, capacity = self._host, self._padded, self.capacity
+
+        def field(name):
+            begin = self._offsets[name][0]
+            return host[begin:begin + capacity]
+
+        field("tokens")[:] = 0
+        field("tokens")[:live] = tokens
+        field("row_seq")[:] = -1
+        field("row_seq")[:live] = np.arange(live, dtype=np.int32)
+        field("row_pos")[:] = 0
+        field("row_pos")[:live] = starts
+        field("seq_slot")[:] = 0
+        field("seq_slot")[:live] = slots
+        field("seq_start")[:] = 0
+        field("seq_start")[:live] = starts
+        field("seq_len")[:] = 1
+        field("seq_row0")[:] = np.arange(capacity, dtype=np.int32)
+        field("want_rows")[:] = np.arange(capacity, dtype=np.int32)
+        field("steps")[:] = 0
+        field("steps")[:live] = steps
+        host[self._temperature_at:self._temperature_at + capacity].view(np.float32)[:] = 0.0
+        host[self._temperature_at:self._temperature_at + live].view(np.float32)[:] = temperature
+        host[self._keys_at:self._keys_at + 2 * capacity].view(np.int64)[:] = 0
+        host[self._keys_at:self._keys_at + 2 * live].view(np.int64)[:] = keys
+        self.buffer.copy_(self.staging, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the staging buffer may be rewritten after this
+        self.live = live
+        self.slots = list(slots)
+        self.positions = list(starts)
+
+    # -------------------------------------------------------------------- step
+    def _forward(self) -> None:
+        engine = self.engine
+        self.logits = engine.model.forward(self._context)
+        self.sampler.select(self.logits, self.temperature, self.keys, self.tables.steps, out=self.selected)
+        ops.advance_decode(self.tables.tokens, self.selected, self.tables.row_seq, self.tables.row_pos,
+                           self.tables.seq_start, self.tables.steps, engine.vocab_size)
+
+    def _capture(self) -> None:
+        """Runs the step once with every row padded (nothing is written to the cache), so
+        that kernels are compiled and configured, then captures it."""
+        saved = self.buffer.clone()
+        begin = self._offsets["row_seq"][0]
+        self.buffer[begin:begin + self.capacity] = -1
+        torch.cuda.synchronize(self.engine.device)
+        with torch.cuda.stream(self._stream):
+            self._forward()
+        self._stream.synchronize()
+        self.buffer.copy_(saved)
+        torch.cuda.synchronize(self.engine.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=self._stream):
+            self._forward()
+        self.buffer.copy_(saved)
+        torch.cuda.synchronize(self.engine.device)
+        # The graph holds the addresses of the scratch buffers it was captured with; they
+        # must outlive it even if the engine later replaces them with larger ones.
+        self._captured_workspaces = dict(self.engine._workspaces)
+
+    def reserve(self, steps: int = 1) -> None:
+        """Makes sure the cache has room for `steps` more tokens of every live sequence."""
+        cache = self.engine.cache
+        cache.reserve([(slot, position + steps) for slot, position in zip(self.slots, self.positions)])
+        cache.flush_tables()
+
+    def launch(self) -> None:
+        """One decode step on the device (no host synchronisation). The caller has reserved room."""
+        if self.graph is None:
+            self._capture()
+        self.graph.replay()
+        self.positions = [position + 1 for position in self.positions]
+        self.engine.cache.commit(list(zip(self.slots, self.positions)))
+
+    def step(self) -> List[int]:
+        """One decode step; returns the selected token of every live sequence."""
+        self.reserve(1)
+        self.launch()
+        self.selected_host.copy_(self.selected, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.selected_host[:self.live].tolist()
+
+
+def _widest_decode(engine) -> Optional[int]:
+    """The key/value head count that decides how decode attention is split (None when
+    no layer has an attention cache)."""
+    heads = [group.request.kv_heads for group in engine.cache.kv_groups]
+    return min(heads) if heads else None

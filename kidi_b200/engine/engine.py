@@ -79,6 +79,7 @@ class Engine:
         self._staging_done = [None, None]  # events: the copy out of the buffer has finished
         self._turn = 0
         self._workspaces: Dict[str, torch.Tensor] = {}
+        self._backends: Dict[tuple, object] = {}
 
     # ---------------------------------------------------------------- loading
     @classmethod
@@ -156,6 +157,29 @@ class Engine:
             logits = self.model.forward(ctx)
             self.cache.commit(growth)
             return logits
+
+    # --------------------------------------------------------------- generation
+    def generate(self, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 0, temperature: float = 0.0,
+                 seed: int = 0, ignore_eos: bool = False, stop_ids: Sequence[int] = (), max_active: int = 0,
+                 context_size: int = 0, prefill_chunk_size: int = 0, use_graph: bool = True,
+                 max_tokens: Optional[Sequence[Optional[int]]] = None, stats=None, detailed: bool = False):
+        """Generates for every prompt (lists of token ids, host integers) and returns the
+        new token ids of each, in order; with `detailed`, `Generation` records instead.
+        The model's own end tokens stop a sequence unless `ignore_eos` is set."""
+        from ..sampling.sampler import Sampler
+        from .generate import DEFAULT_MAX_ACTIVE, EngineBackend, GenerationOptions, generate
+        with torch.cuda.device(self.device):
+            options = GenerationOptions(
+                max_new_tokens=max_new_tokens, context_size=context_size, prefill_chunk_size=prefill_chunk_size,
+                temperature=temperature, seed=seed, ignore_eos=ignore_eos, stop_ids=tuple(stop_ids),
+                max_active=max_active or DEFAULT_MAX_ACTIVE, use_graph=use_graph)
+            key = (seed, use_graph)
+            backend = self._backends.get(key)
+            if backend is None:
+                backend = self._backends[key] = EngineBackend(self, Sampler(seed), use_graph)
+            found = generate(backend, prompts, options, stop_ids=self.spec.eos_token_ids, max_tokens=max_tokens,
+                             stats=stats)
+        return found if detailed else [generation.token_ids for generation in found]
 
     # ------------------------------------------------------------- accounting
     def memory(self) -> Dict[str, int]:

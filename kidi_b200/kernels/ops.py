@@ -74,8 +74,10 @@ def core():
         lib.kidi_argmax.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.kidi_sample.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_ulonglong, c_void_p, c_void_p,
                                     c_void_p]
+        lib.kidi_advance_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                            c_void_p]
         for name in ("kidi_embedding", "kidi_add_rmsnorm", "kidi_silu_gate", "kidi_gemm_simt", "kidi_rope_store",
-                     "kidi_attention_generic", "kidi_argmax", "kidi_sample"):
+                     "kidi_attention_generic", "kidi_argmax", "kidi_sample", "kidi_advance_decode"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core
@@ -272,3 +274,16 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: int, keys: tor
                               ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _ptr(keys), _ptr(steps), _stream()),
            "sample")
     return out
+
+
+def advance_decode(tokens: torch.Tensor, selected: torch.Tensor, row_seq: torch.Tensor, row_pos: torch.Tensor,
+                   seq_start: torch.Tensor, steps: torch.Tensor, vocab: int) -> None:
+    """After a decode step: every live row takes its selected token as its next input
+    and moves one position on (tokens, positions and step counters change in place)."""
+    _need_cuda(tokens, selected, row_seq, row_pos, seq_start, steps)
+    rows = tokens.shape[0]
+    for tensor in (tokens, selected, row_seq, row_pos, seq_start, steps):
+        if tensor.dtype != torch.int32 or tensor.shape[0] < rows:
+            raise invalid_argument("advance_decode takes int32 vectors of one length")
+    _check(core().kidi_advance_decode(_ptr(tokens), _ptr(selected), _ptr(row_seq), _ptr(row_pos), _ptr(seq_start),
+                                      _ptr(steps), rows, vocab, _stream()), "advance_decode")

@@ -15,7 +15,7 @@ from ..errors import invalid_argument
 from . import ops
 from .ops import _check, _need_cuda, _ptr, _stream, c_int, c_longlong, c_void_p, dtype_code
 
-MAX_ROWS = int(os.environ.get("KIDI_B200_SKINNY_MAX_ROWS", "64"))
+MAX_ROWS = int(os.environ.get("KIDI_B200_SKINNY_MAX_ROWS", "8"))
 
 _bound = False
 

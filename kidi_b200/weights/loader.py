@@ -143,6 +143,7 @@ def bind_parameters(params: Sequence[Tuple[str, ParamSpec]], source, *, engine_d
                 plans.append((full, names, spec))
                 consumed.update(name for name, _ in names)
                 continue
+            consumed.update(name for name, _ in names if name in source)  # expected, though incomplete
             if spec.alias_of is None:
                 missing.extend(absent)
                 continue
