@@ -1,0 +1,289 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the library on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+
+A step is one decode step of the batch. The default run is the Qwen3-8B shape (every
+layer size, all 36 layers) with random bfloat16 weights drawn on the device from a
+seed, a batch of 8 sequences with 1,024-token prompts of uniform token ids, then decoding.
+It prints ONE line of JSON:
+
+* `value`: decoded tokens a second, timed on the device with CUDA events over exactly K
+  steps after W warm-up steps (tokens selected and fed back on the device);
+* `e2e`: the same through the Python entry point (`Engine.generate`): host token ids in
+  and out, every step copying its input tokens from pinned host memory and reading its
+  selected tokens back;
+* `prefill`: one 2,048-token prompt: tokens a second, milliseconds, and the fraction of
+  the bfloat16 tensor-core peak its FLOPs reach;
+* `roofline`: the decode step's bytes (every weight it uses once, plus the cache of the
+  live sequences) over its time, against the measured HBM copy bandwidth;
+* `points`: decode tokens a second at batch 1 and 64.
+
+Every decode step reads about 16 GB of weights and cache, far more than the 126 MB L2, so
+no L2 flush is needed between timed steps. Peaks come from MEASURED_PEAKS.json beside
+this file when the driver wrote it. The reference arm cannot run here: the reference
+does not build without its third-party submodules.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu",
+    "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 40960, "attention_bias": False,
+}
+PROMPT_TOKENS = 1024
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as handle:
+            found = json.load(handle)
+        hbm = float(found.get("hbm_gbs") or found.get("hbm_gb_s"))
+        tflops = float(found.get("bf16_tflops"))
+        return {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": "measured"}
+    except (OSError, ValueError, TypeError, KeyError):
+        return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.lines, self.process, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.process = None
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.process.terminate()
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            fields = [field.strip() for field in line.split(",")]
+            if len(fields) < 6 or not fields[0].isdigit():
+                continue
+            clocks.append(int(fields[0]))
+            maxima.append(int(fields[1]))
+            reasons.update(name for name, field in zip(names, fields[2:6]) if field.lower().startswith("active"))
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def decode_bytes(config: dict, batch: int, context: float) -> float:
+    """Bytes a decode step has to read: every weight it uses once (bfloat16), the
+    embedding rows of the batch, and the keys and values of the live sequences."""
+    hidden, inter, layers = config["hidden_size"], config["intermediate_size"], config["num_hidden_layers"]
+    q = config["num_attention_heads"] * config["head_dim"]
+    kv = config["num_key_value_heads"] * config["head_dim"]
+    per_layer = hidden * (q + 2 * kv) + q * hidden + 3 * hidden * inter + 2 * hidden + 2 * config["head_dim"]
+    weights = 2 * (layers * per_layer + config["vocab_size"] * hidden + hidden + batch * hidden)
+    cache = 2 * layers * 2 * kv * context * batch
+    return float(weights + cache)
+
+
+def prefill_flops(config: dict, tokens: int) -> float:
+    hidden, inter, layers = config["hidden_size"], config["intermediate_size"], config["num_hidden_layers"]
+    q = config["num_attention_heads"] * config["head_dim"]
+    kv = config["num_key_value_heads"] * config["head_dim"]
+    linear = 2.0 * tokens * layers * (hidden * (q + 2 * kv) + q * hidden + 3 * hidden * inter)
+    attention = layers * 4.0 * q * tokens * (tokens + 1) / 2
+    head = 2.0 * config["vocab_size"] * hidden
+    return linear + attention + head
+
+
+def time_decode(engine, sampler, batch: int, steps: int, warmup: int, seed: int, clocks: bool):
+    """Device-timed decode: prompts in one step, then `warmup` + `steps` replayed steps
+    with tokens selected and fed back on the device. Returns a dict of measurements."""
+    import numpy as np
+    import torch
+    from kidi_b200 import StepBatch
+    from kidi_b200.engine.decode_graph import DecodeSession
+    from kidi_b200.kernels import ops
+
+    generator = np.random.default_rng(seed)
+    prompts = generator.integers(0, engine.vocab_size, size=(batch, PROMPT_TOKENS)).tolist()
+    slots = [engine.acquire() for _ in range(batch)]
+    try:
+        logits = engine.step(StepBatch(slots, prompts, None))
+        first = sampler.select(logits).cpu().tolist()
+        session = DecodeSession(engine, batch, sampler, longest=PROMPT_TOKENS + warmup + steps + 1)
+        session.load(slots, first, [0.0] * batch, list(range(batch)), [1] * batch)
+        session.reserve(warmup + steps)
+        for _ in range(warmup):
+            session.launch()
+        torch.cuda.synchronize()
+        sampler_thread = ClockSampler() if clocks else None
+        if sampler_thread:
+            sampler_thread.start()
+            time.sleep(0.25)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(steps):
+            session.launch()
+        end.record()
+        torch.cuda.synchronize()
+        elapsed_ms = begin.elapsed_time(end)
+        clock_record = sampler_thread.stop() if sampler_thread else None
+        return {"ms_per_step": elapsed_ms / steps, "tokens_per_s": batch * steps / (elapsed_ms / 1e3),
+                "kernels_per_step": session.kernels_per_step, "clocks": clock_record,
+                "mean_context": PROMPT_TOKENS + warmup + (steps + 1) / 2}
+    finally:
+        for slot in slots:
+            engine.release(slot)
+
+
+def time_prefill(engine, seed: int, repeats: int = 5):
+    import numpy as np
+    import torch
+    from kidi_b200 import StepBatch
+
+    generator = np.random.default_rng(seed)
+    prompt = generator.integers(0, engine.vocab_size, size=PREFILL_TOKENS).tolist()
+    times = []
+    for index in range(repeats + 2):
+        slot = engine.acquire()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        engine.step(StepBatch([slot], [prompt], None))
+        end.record()
+        torch.cuda.synchronize()
+        engine.release(slot)
+        if index >= 2:  # two warm-up runs
+            times.append(begin.elapsed_time(end))
+    return statistics.median(times)
+
+
+def time_end_to_end(engine, batch: int, steps: int, seed: int):
+    """Decode tokens a second through `Engine.generate`: host token ids in and out."""
+    import numpy as np
+    from kidi_b200.engine.generate import GenerationStats
+
+    generator = np.random.default_rng(seed + 1)
+    prompts = generator.integers(0, engine.vocab_size, size=(batch, PROMPT_TOKENS)).tolist()
+    engine.generate(prompts, max_new_tokens=4, ignore_eos=True, max_active=batch)   # captures the graph
+    stats = GenerationStats()
+    engine.generate(prompts, max_new_tokens=steps + 1, ignore_eos=True, max_active=batch, stats=stats)
+    return batch * stats.decode_steps / (stats.decode_ns / 1e9), stats
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=256)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference does not build offline: its CMake stops at 'yaml-cpp is missing from "
+                          "third_party' (empty submodules), and its Qwen3 is an INT8 bidirectional backbone "
+                          "without cache, head or generation"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this library is single-GPU by design (asked for {args.gpus})")
+        return 2
+    if args.steps < 1 or args.warmup < 3:
+        print("bench.py needs --steps >= 1 and --warmup >= 3")
+        return 2
+
+    import torch
+    from kidi_b200 import Engine
+    from kidi_b200.sampling.sampler import Sampler
+
+    config = dict(QWEN3_8B)
+    full_layers = config["num_hidden_layers"]
+    if args.layers:
+        config["num_hidden_layers"] = args.layers
+    largest = max(args.batch, 1 if args.skip_points else 64)
+    per_sequence = PROMPT_TOKENS + args.warmup + args.steps + 2
+    budget = max(largest * (-(-per_sequence // 64) * 64), 4096)
+    engine = Engine.from_config(config, seed=args.seed, dtype="bfloat16", device="cuda:0", max_tokens=budget)
+    sampler = Sampler(args.seed)
+    peak = peaks()
+
+    main_run = time_decode(engine, sampler, args.batch, args.steps, args.warmup, args.seed, clocks=True)
+    e2e_value, e2e_stats = time_end_to_end(engine, args.batch, args.steps, args.seed)
+    points, prefill = {}, None
+    if not args.skip_points:
+        short = min(args.steps, 128)
+        for batch in (1, 64):
+            run = time_decode(engine, sampler, batch, short, args.warmup, args.seed + batch, clocks=False)
+            points[f"decode_b{batch}"] = round(run["tokens_per_s"], 1)
+        prefill_ms = time_prefill(engine, args.seed)
+        flops = prefill_flops(config, PREFILL_TOKENS)
+        prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "unit": "tokens/s",
+                   "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
+                   "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
+                   "tflops": round(flops / (prefill_ms / 1e3) / 1e12, 1)}
+
+    achieved = decode_bytes(config, args.batch, main_run["mean_context"]) / (main_run["ms_per_step"] / 1e3) / 1e9
+    record = {
+        "metric": "decode tokens/s (Qwen3-8B shape, bf16, batch 8, 1024-token prompts)",
+        "value": round(main_run["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) from a seed, uniform token ids", "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B shape", "layers": config["num_hidden_layers"], "layers_of_model": full_layers,
+            "hidden_size": config["hidden_size"], "heads": config["num_attention_heads"],
+            "kv_heads": config["num_key_value_heads"], "head_dim": config["head_dim"],
+            "intermediate_size": config["intermediate_size"], "vocab_size": config["vocab_size"],
+            "rope_theta": config["rope_theta"], "rms_norm_eps": config["rms_norm_eps"],
+            "tie_word_embeddings": False, "global_batch": args.batch, "prompt_tokens": PROMPT_TOKENS,
+            "context_per_sequence": 4096, "seq_len": int(main_run["mean_context"]), "parallelism": "single GPU",
+            "l2": "no flush: a step reads ~16 GB, the L2 holds 126 MB", "peaks": peak["source"],
+        },
+        "clocks": main_run["clocks"],
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
+                "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_stats.decode_steps},
+        "gpu_launches": main_run["kernels_per_step"] * args.steps,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "of": peak["source"]},
+    }
+    if prefill:
+        record["prefill"] = prefill
+    if points:
+        record["points"] = points
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

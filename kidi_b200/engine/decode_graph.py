@@ -54,6 +54,7 @@ class DecodeSession:
         self._keys_at = base + padded
         self.selected = torch.zeros(capacity, dtype=torch.int32, device=device)
         self.selected_host = torch.zeros(capacity, dtype=torch.int32).pin_memory()
+        self.tokens_host = torch.zeros(capacity, dtype=torch.int32).pin_memory()
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.live = 0
@@ -136,8 +137,10 @@ class DecodeSession:
         self.buffer.copy_(saved)
         torch.cuda.synchronize(self.engine.device)
         self.graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
         with torch.cuda.graph(self.graph, stream=self._stream):
             self._forward()
+        self.kernels_per_step = ops.launch_count - before   # this package's kernels in one replay
         self.buffer.copy_(saved)
         torch.cuda.synchronize(self.engine.device)
         # The graph holds the addresses of the scratch buffers it was captured with; they
@@ -158,9 +161,15 @@ class DecodeSession:
         self.positions = [position + 1 for position in self.positions]
         self.engine.cache.commit(list(zip(self.slots, self.positions)))
 
-    def step(self) -> List[int]:
-        """One decode step; returns the selected token of every live sequence."""
+    def step(self, tokens: Optional[Sequence[int]] = None) -> List[int]:
+        """One decode step; returns the selected token of every live sequence. With
+        `tokens` (host integers, one per live sequence) the step's inputs are copied from
+        pinned host memory first; without, the tokens selected by the previous step are
+        used where they lie on the device."""
         self.reserve(1)
+        if tokens is not None:
+            self.tokens_host[:self.live] = torch.as_tensor(tokens, dtype=torch.int32)
+            self.tables.tokens[:self.live].copy_(self.tokens_host[:self.live], non_blocking=True)
         self.launch()
         self.selected_host.copy_(self.selected, non_blocking=True)
         torch.cuda.current_stream().synchronize()

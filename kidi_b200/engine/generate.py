@@ -112,8 +112,10 @@ class _EagerDecode:
         self.backend, self.slots, self.tokens = backend, list(slots), list(tokens)
         self.temperature, self.keys, self.steps = list(temperature), list(keys), list(steps)
 
-    def step(self) -> List[int]:
+    def step(self, tokens: Optional[Sequence[int]] = None) -> List[int]:
         engine, sampler = self.backend.engine, self.backend.sampler
+        if tokens is not None:
+            self.tokens = list(tokens)
         logits = engine.step(StepBatch(self.slots, [[token] for token in self.tokens], None))
         self.tokens = sampler.select_host(logits, self.temperature, self.keys, self.steps)
         self.steps = [step + 1 for step in self.steps]
@@ -201,7 +203,7 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], options: Genera
                     session = backend.open_decode([slots[i] for i in live], [states[i].token for i in live],
                                                   [options.temperature] * len(live), live,
                                                   [states[i].steps for i in live], longest)
-                chosen = session.step()
+                chosen = session.step([states[i].token for i in live])
                 stats.decode_steps += 1
                 for i, token in zip(live, chosen):
                     states[i].accept(token)

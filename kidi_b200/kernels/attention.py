@@ -95,6 +95,6 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
             args.partial_out = workspace.data_ptr()
             args.partial_stat = workspace.data_ptr() + qkv.shape[0] * heads * splits * head_dim * 4
         args.splits = splits
-        _check(lib.kidi_attention_decode(ctypes.byref(args), stream), "attention_decode")
+        _check(lib.kidi_attention_decode(ctypes.byref(args), stream), "attention_decode", 2 if splits > 1 else 1)
     else:
         _check(lib.kidi_attention_prefill(ctypes.byref(args), plan.max_new, stream), "attention_prefill")

@@ -43,8 +43,13 @@ def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
             raise runtime_error("the kernels run on a CUDA device only (there is no CPU path)")
 
 
-def _check(status: int, what: str) -> None:
+launch_count = 0  # kernels of this package launched (or captured into a graph) so far
+
+
+def _check(status: int, what: str, launches: int = 1) -> None:
+    global launch_count
     if status == 0:
+        launch_count += launches
         return
     if status == -2:
         raise unsupported(f"{what}: this combination of element types is not compiled")

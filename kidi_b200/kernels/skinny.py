@@ -31,11 +31,18 @@ def _library():
     return lib
 
 
-def fits(x: torch.Tensor, weight: torch.Tensor) -> bool:
+def supports(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the kernel can take the product at all (up to 64 rows)."""
     return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and weight.dim() == 2
-            and 0 < x.shape[0] <= MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
+            and 0 < x.shape[0] <= 64 and x.shape[1] % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
             and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and weight.data_ptr() % 16 == 0)
+
+
+def fits(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the product should take this kernel: it can, and it has few enough rows
+    for streaming the weights once to beat the matrix library."""
+    return x.dim() == 2 and x.shape[0] <= MAX_ROWS and supports(x, weight)
 
 
 def _row_tiles(features: int) -> int:
@@ -48,7 +55,7 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Opt
          row_tiles: Optional[int] = None) -> torch.Tensor:
     """y = x @ weight.T for x [M <= 64, K], weight [N, K], both bfloat16."""
     _need_cuda(x, weight)
-    if not fits(x, weight) or x.shape[1] != weight.shape[1]:
+    if not supports(x, weight) or x.shape[1] != weight.shape[1]:
         raise invalid_argument("gemm_skinny: the operands do not fit this kernel")
     M, K = x.shape
     N = weight.shape[0]
@@ -63,7 +70,7 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Opt
 def gemm_silu_gate(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) for weight = [Wg; Wu] of shape [2I, K]."""
     _need_cuda(x, weight)
-    if not fits(x, weight) or x.shape[1] != weight.shape[1] or weight.shape[0] % 2:
+    if not supports(x, weight) or x.shape[1] != weight.shape[1] or weight.shape[0] % 2:
         raise invalid_argument("gemm_silu_gate: the operands do not fit this kernel")
     M, K = x.shape
     inter = weight.shape[0] // 2

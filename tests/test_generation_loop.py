@@ -49,7 +49,8 @@ class FakeBackend:
             def __init__(self):
                 self.tokens = list(tokens)
 
-            def step(self):
+            def step(self, fed=None):
+                assert fed is None or list(fed) == self.tokens   # the loop feeds back what it was given
                 for slot, token in zip(slots, self.tokens):
                     backend.sequences[slot].append(token)
                 self.tokens = [backend._next(slot) for slot in slots]
