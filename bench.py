@@ -121,7 +121,8 @@ def prefill_flops(config: dict, tokens: int) -> float:
     return linear + attention + head
 
 
-def time_decode(engine, sampler, batch: int, steps: int, warmup: int, seed: int, clocks: bool):
+def time_decode(engine, sampler, batch: int, steps: int, warmup: int, seed: int, clocks: bool,
+                profile_steps: int = 0):
     """Device-timed decode: prompts in one step, then `warmup` + `steps` replayed steps
     with tokens selected and fed back on the device. Returns a dict of measurements."""
     import numpy as np
@@ -155,6 +156,13 @@ def time_decode(engine, sampler, batch: int, steps: int, warmup: int, seed: int,
         torch.cuda.synchronize()
         elapsed_ms = begin.elapsed_time(end)
         clock_record = sampler_thread.stop() if sampler_thread else None
+        if profile_steps:  # a few more steps inside a profiler range (ncu --profile-from-start off)
+            session.reserve(profile_steps)
+            torch.cuda.profiler.start()
+            for _ in range(profile_steps):
+                session.launch()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
         return {"ms_per_step": elapsed_ms / steps, "tokens_per_s": batch * steps / (elapsed_ms / 1e3),
                 "kernels_per_step": session.kernels_per_step, "clocks": clock_record,
                 "mean_context": PROMPT_TOKENS + warmup + (steps + 1) / 2}
@@ -163,7 +171,7 @@ def time_decode(engine, sampler, batch: int, steps: int, warmup: int, seed: int,
             engine.release(slot)
 
 
-def time_prefill(engine, seed: int, repeats: int = 5):
+def time_prefill(engine, seed: int, repeats: int = 5, profile: bool = False):
     import numpy as np
     import torch
     from kidi_b200 import StepBatch
@@ -182,6 +190,13 @@ def time_prefill(engine, seed: int, repeats: int = 5):
         engine.release(slot)
         if index >= 2:  # two warm-up runs
             times.append(begin.elapsed_time(end))
+    if profile:
+        slot = engine.acquire()
+        torch.cuda.profiler.start()
+        engine.step(StepBatch([slot], [prompt], None))
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        engine.release(slot)
     return statistics.median(times)
 
 
@@ -208,6 +223,11 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
+    parser.add_argument("--skip-e2e", action="store_true", help="leave out the end-to-end run (profiling)")
+    parser.add_argument("--profile-steps", type=int, default=0,
+                        help="run this many extra decode steps inside cudaProfilerStart/Stop")
+    parser.add_argument("--profile-prefill", action="store_true",
+                        help="run one extra 2,048-token prefill inside cudaProfilerStart/Stop")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -238,8 +258,15 @@ def main() -> int:
     sampler = Sampler(args.seed)
     peak = peaks()
 
-    main_run = time_decode(engine, sampler, args.batch, args.steps, args.warmup, args.seed, clocks=True)
-    e2e_value, e2e_stats = time_end_to_end(engine, args.batch, args.steps, args.seed)
+    main_run = time_decode(engine, sampler, args.batch, args.steps, args.warmup, args.seed, clocks=True,
+                           profile_steps=args.profile_steps)
+    if args.skip_e2e:
+        from kidi_b200.engine.generate import GenerationStats
+        e2e_value, e2e_stats = 0.0, GenerationStats()
+    else:
+        e2e_value, e2e_stats = time_end_to_end(engine, args.batch, args.steps, args.seed)
+    if args.profile_prefill:
+        time_prefill(engine, args.seed, repeats=1, profile=True)
     points, prefill = {}, None
     if not args.skip_points:
         short = min(args.steps, 128)

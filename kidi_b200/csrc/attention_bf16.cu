@@ -19,6 +19,8 @@
 // src/kidi/model/gemma4.cpp:736-740.
 #include "common.cuh"
 
+KIDI_DEFINE_PDL_FLAG()
+
 #ifndef KIDI_HEAD_DIM
 #error "compile with -DKIDI_HEAD_DIM=<head width>"
 #endif
@@ -212,6 +214,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(Args a) {
     bf16* q_tile = reinterpret_cast<bf16*>(raw);            // [64][PITCH]
     bf16* k_tiles = q_tile + TILE * PITCH;                  // [2][64][PITCH]
     bf16* v_tiles = k_tiles + 2 * TILE * PITCH;             // [2][64][PITCH]
+    pdl_prologue();
     const int seq = blockIdx.y, head = blockIdx.z;
     const int q0 = blockIdx.x * TILE;
     const int count = a.seq_len[seq];
@@ -325,6 +328,20 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
         tile_first = tile_low + split * per_split;
         tiles = max(0, min(per_split, tile_high + 1 - tile_first));
     }
+    // The pages of this block do not depend on the kernel before this one, except for the
+    // newest token's row: they are asked into L2 before the wait for that kernel; the loads
+    // into shared memory, and the query, come after it.
+    pdl_launch_dependents();
+#ifndef KIDI_ATTN_PREFETCH
+#define KIDI_ATTN_PREFETCH 0
+#endif
+    for (int line = threadIdx.x; KIDI_ATTN_PREFETCH && line < tiles * (TILE * D * 2 / 128); line += THREADS) {
+        const int index = line / (TILE * D * 2 / 128), within = line - index * (TILE * D * 2 / 128);
+        const long long offset = cache_row_offset(a.cache, slot, (tile_first + index) * TILE, kv_head) + within * 64;
+        prefetch_l2(a.k_cache + offset);
+        prefetch_l2(a.v_cache + offset);
+    }
+    pdl_wait();
     if (tiles > 0) {
         for (int chunk = threadIdx.x; chunk < 16 * CHUNKS; chunk += THREADS) {
             const int r = chunk / CHUNKS, c = chunk - r * CHUNKS;
@@ -414,6 +431,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
 
 // grid (heads, rows): merges the splits of one (row, head) in split order.
 __global__ void attention_combine_kernel(Args a) {
+    pdl_prologue();
     const int head = blockIdx.x, row = blockIdx.y;
     const long long where = ((long long)row * a.heads + head) * a.splits;
     float top = -INFINITY;
@@ -459,8 +477,7 @@ KIDI_API int kidi_attention_prefill(const Args* args, int max_new, cudaStream_t 
         configured = true;
     }
     dim3 grid((max_new + TILE - 1) / TILE, a.seqs, a.heads);
-    attention_prefill_kernel<<<grid, THREADS, PREFILL_SHARED, stream>>>(a);
-    return kidi_launch_status();
+    return kidi_launch(attention_prefill_kernel, grid, THREADS, PREFILL_SHARED, stream, a);
 }
 
 // One query row per sequence; every key comes from the cache. With splits > 1 the
@@ -480,10 +497,8 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(a.splits, a.kv_heads, a.rows);
-    attention_decode_kernel<<<grid, THREADS, DECODE_SHARED, stream>>>(a);
-    int status = kidi_launch_status();
+    int status = kidi_launch(attention_decode_kernel, grid, THREADS, DECODE_SHARED, stream, a);
     if (status || a.splits == 1) return status;
     dim3 combine(a.heads, a.rows);
-    attention_combine_kernel<<<combine, D >= 128 ? 128 : 64, 0, stream>>>(a);
-    return kidi_launch_status();
+    return kidi_launch(attention_combine_kernel, combine, D >= 128 ? 128 : 64, 0, stream, a);
 }

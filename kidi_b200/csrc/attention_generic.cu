@@ -41,6 +41,7 @@ struct RopeStoreArgs {
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128) rope_store_kernel(RopeStoreArgs a) {
     __shared__ float normed[4][256];
+    pdl_prologue();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_heads = a.heads + 2 * a.kv_heads;
     const long long item = (long long)blockIdx.x * 4 + warp;
@@ -120,12 +121,11 @@ KIDI_API int kidi_rope_store(const RopeStoreArgs* args, int dtype, int norm_dtyp
     if (a.head_dim > 256 || a.head_dim <= 0 || a.rotary_dim > a.head_dim || (a.rotary_dim & 1)) return KIDI_REFUSED_SIZE;
     const long long items = (long long)a.rows * (a.heads + 2 * a.kv_heads);
     const unsigned blocks = (unsigned)((items + 3) / 4);
-    if (dtype == KIDI_F32 && norm_dtype == KIDI_F32) rope_store_kernel<float, float><<<blocks, 128, 0, stream>>>(a);
-    else if (dtype == KIDI_F32 && norm_dtype == KIDI_BF16) rope_store_kernel<float, bf16><<<blocks, 128, 0, stream>>>(a);
-    else if (dtype == KIDI_BF16 && norm_dtype == KIDI_F32) rope_store_kernel<bf16, float><<<blocks, 128, 0, stream>>>(a);
-    else if (dtype == KIDI_BF16 && norm_dtype == KIDI_BF16) rope_store_kernel<bf16, bf16><<<blocks, 128, 0, stream>>>(a);
-    else return KIDI_REFUSED_DTYPE;
-    return kidi_launch_status();
+    if (dtype == KIDI_F32 && norm_dtype == KIDI_F32) return kidi_launch(rope_store_kernel<float, float>, blocks, 128, 0, stream, a);
+    if (dtype == KIDI_F32 && norm_dtype == KIDI_BF16) return kidi_launch(rope_store_kernel<float, bf16>, blocks, 128, 0, stream, a);
+    if (dtype == KIDI_BF16 && norm_dtype == KIDI_F32) return kidi_launch(rope_store_kernel<bf16, float>, blocks, 128, 0, stream, a);
+    if (dtype == KIDI_BF16 && norm_dtype == KIDI_BF16) return kidi_launch(rope_store_kernel<bf16, bf16>, blocks, 128, 0, stream, a);
+    return KIDI_REFUSED_DTYPE;
 }
 
 // ---------------------------------------------------------------------------
@@ -158,6 +158,7 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(AttentionArgs a)
     __shared__ float query[256];
     __shared__ float part_acc[4][256];
     __shared__ float part_max[4], part_sum[4];
+    pdl_prologue();
     const int row = blockIdx.x, head = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d = a.head_dim;
@@ -239,8 +240,7 @@ KIDI_API int kidi_attention_generic(const AttentionArgs* args, int dtype, cudaSt
     if (a.rows <= 0) return 0;
     if (a.head_dim > 256 || a.head_dim <= 0 || a.heads % a.kv_heads || a.heads > 65535) return KIDI_REFUSED_SIZE;
     dim3 grid(a.rows, a.heads);
-    if (dtype == KIDI_F32) attention_generic_kernel<float><<<grid, 128, 0, stream>>>(a);
-    else if (dtype == KIDI_BF16) attention_generic_kernel<bf16><<<grid, 128, 0, stream>>>(a);
-    else return KIDI_REFUSED_DTYPE;
-    return kidi_launch_status();
+    if (dtype == KIDI_F32) return kidi_launch(attention_generic_kernel<float>, grid, 128, 0, stream, a);
+    if (dtype == KIDI_BF16) return kidi_launch(attention_generic_kernel<bf16>, grid, 128, 0, stream, a);
+    return KIDI_REFUSED_DTYPE;
 }

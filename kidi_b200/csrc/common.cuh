@@ -75,3 +75,50 @@ __device__ __forceinline__ long long cache_row_offset(const CacheGeometry& g, in
 }
 
 static inline int kidi_launch_status() { return (int)cudaGetLastError(); }
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch (off unless kidi_set_pdl(1) is called; measured on
+// B200 inside a captured decode step it made the step slower, 5.9 ms against 4.2 ms, so
+// it is kept as an experiment switch only). With it, every kernel of this package is
+// launched with "programmatic stream serialization": it may become resident while the
+// kernel before it in the stream is still running, and it calls pdl_wait() before it
+// reads or writes anything an earlier kernel of the same step touches. What it does before
+// that (index arithmetic, reading weights and the step's integer tables, prefetching
+// weights into L2) overlaps the tail of its predecessor, which hides the launch
+// latency of the few hundred small kernels of a decode step. pdl_wait() returns when
+// the preceding kernel has completed and its writes are visible, so the chain of
+// kernels keeps the order of the stream. Memory that is only written between graph
+// launches (weights, block tables) or by the last kernel of the previous step
+// (positions) may be read before the wait.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_prologue() {
+    pdl_launch_dependents();
+    pdl_wait();
+}
+__device__ __forceinline__ void prefetch_l2(const void* pointer) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(pointer));
+}
+
+extern int kidi_pdl_flag;  // one per library; 0 launches every kernel the ordinary way
+
+#define KIDI_DEFINE_PDL_FLAG()                                              \
+    int kidi_pdl_flag = 0;                                                  \
+    KIDI_API void kidi_set_pdl(int enabled) { kidi_pdl_flag = enabled; }
+
+template <typename... Expected, typename... Actual>
+static inline int kidi_launch(void (*kernel)(Expected...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
+                              Actual&&... arguments) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = kidi_pdl_flag ? 1 : 0;
+    cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<Expected>(arguments)...);
+    return status != cudaSuccess ? (int)status : (int)cudaGetLastError();
+}

@@ -1,4 +1,5 @@
-// Embedding gather, residual-add + RMSNorm, and the SiLU gate.
+// Embedding gather, residual-add + RMSNorm, the SiLU gate, and the bookkeeping kernel
+// that advances a decode step.
 //
 // Formulas (reference): embedding row gather times a scalar scale
 // (src/kidi/layers/gemma4.cpp:97-99,132-142); RMSNorm y = x * (1/sqrt(sum(x^2)/H + eps)) * w
@@ -7,10 +8,13 @@
 // 32-bit in every engine dtype, and the sum of squares and the inverse root are 32-bit.
 #include "common.cuh"
 
+KIDI_DEFINE_PDL_FLAG()
+
 // ------------------------------------------------------------------ embedding
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                  const int* __restrict__ tokens, int hidden, int vocab, float scale) {
+    pdl_prologue();
     const int row = blockIdx.x;
     const int token = tokens[row];
     float* destination = out + (long long)row * hidden;
@@ -27,12 +31,12 @@ KIDI_API int kidi_embedding(float* out, const void* table, int table_dtype, cons
     if (rows <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == KIDI_F32)
-        embedding_kernel<float><<<rows, threads, 0, stream>>>(out, (const float*)table, tokens, hidden, vocab, scale);
-    else if (table_dtype == KIDI_BF16)
-        embedding_kernel<bf16><<<rows, threads, 0, stream>>>(out, (const bf16*)table, tokens, hidden, vocab, scale);
-    else
-        return KIDI_REFUSED_DTYPE;
-    return kidi_launch_status();
+        return kidi_launch(embedding_kernel<float>, rows, threads, 0, stream, out, (const float*)table, tokens, hidden,
+                           vocab, scale);
+    if (table_dtype == KIDI_BF16)
+        return kidi_launch(embedding_kernel<bf16>, rows, threads, 0, stream, out, (const bf16*)table, tokens, hidden,
+                           vocab, scale);
+    return KIDI_REFUSED_DTYPE;
 }
 
 // ------------------------------------------------------- residual add + RMSNorm
@@ -47,6 +51,7 @@ add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, c
                    TY* __restrict__ y, const int* __restrict__ row_index, int hidden, float eps, int write_residual) {
     extern __shared__ float staged[];
     __shared__ float scratch[32];
+    pdl_prologue();
     const int r = blockIdx.x;
     const long long s = row_index ? row_index[r] : r;
     float* h = residual + s * hidden;
@@ -76,9 +81,8 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const void* we
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (status != cudaSuccess) return (int)status;
     }
-    kernel<<<rows, THREADS, shared, stream>>>(residual, (const TD*)delta, (const TW*)weight, (TY*)y, row_index,
-                                               hidden, eps, write_residual);
-    return kidi_launch_status();
+    return kidi_launch(kernel, rows, THREADS, shared, stream, residual, (const TD*)delta, (const TW*)weight, (TY*)y,
+                       row_index, hidden, eps, write_residual);
 }
 
 // delta_dtype may be KIDI_NONE (no delta). The residual is always float.
@@ -110,6 +114,7 @@ KIDI_API int kidi_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
 __global__ void advance_decode_kernel(int* __restrict__ tokens, const int* __restrict__ selected,
                                       const int* __restrict__ row_seq, int* __restrict__ row_pos,
                                       int* __restrict__ seq_start, int* __restrict__ steps, int rows, int vocab) {
+    pdl_prologue();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows || row_seq[r] < 0) return;
     const int token = selected[r];
@@ -122,15 +127,15 @@ __global__ void advance_decode_kernel(int* __restrict__ tokens, const int* __res
 KIDI_API int kidi_advance_decode(int* tokens, const int* selected, const int* row_seq, int* row_pos, int* seq_start,
                                  int* steps, int rows, int vocab, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    advance_decode_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(tokens, selected, row_seq, row_pos, seq_start, steps,
-                                                                  rows, vocab);
-    return kidi_launch_status();
+    return kidi_launch(advance_decode_kernel, (rows + 127) / 128, 128, 0, stream, tokens, selected, row_seq, row_pos,
+                       seq_start, steps, rows, vocab);
 }
 
 // ------------------------------------------------------------------ SiLU gate
 // gate_up [rows, 2*inter] (gate = first inter columns, up = last inter) -> out [rows, inter]
 template <typename T>
 __global__ void silu_gate_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter) {
+    pdl_prologue();
     const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (index >= total) return;
     const long long row = index / inter;
@@ -146,10 +151,10 @@ KIDI_API int kidi_silu_gate(const void* gate_up, void* out, int dtype, int rows,
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == KIDI_F32)
-        silu_gate_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, inter);
-    else if (dtype == KIDI_BF16)
-        silu_gate_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, inter);
-    else
-        return KIDI_REFUSED_DTYPE;
-    return kidi_launch_status();
+        return kidi_launch(silu_gate_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out,
+                           total, inter);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(silu_gate_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total,
+                           inter);
+    return KIDI_REFUSED_DTYPE;
 }

@@ -19,6 +19,7 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restr
                  long long ldx, long long ldw, long long ldy) {
     __shared__ float xs[TILE_K][TILE + PAD];
     __shared__ float ws[TILE_K][TILE + PAD];
+    pdl_prologue();
     const int tx = threadIdx.x & 15;   // 4 output columns (n) each
     const int ty = threadIdx.x >> 4;   // 4 output rows (m) each
     const int m0 = blockIdx.y * TILE, n0 = blockIdx.x * TILE;
@@ -69,8 +70,8 @@ template <typename TX, typename TW, typename TY>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw, long long ldy,
            cudaStream_t stream) {
     dim3 grid((N + TILE - 1) / TILE, (M + TILE - 1) / TILE);
-    gemm_simt_kernel<TX, TW, TY><<<grid, 256, 0, stream>>>((const TX*)x, (const TW*)w, (TY*)y, M, N, K, ldx, ldw, ldy);
-    return kidi_launch_status();
+    return kidi_launch(gemm_simt_kernel<TX, TW, TY>, grid, 256, 0, stream, (const TX*)x, (const TW*)w, (TY*)y, M, N, K,
+                       ldx, ldw, ldy);
 }
 }  // namespace
 

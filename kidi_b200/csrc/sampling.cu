@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
                                                          int vocab) {
     __shared__ Best scratch[THREADS / 32];
     __shared__ int invalid;
+    pdl_prologue();
     const Best best = block_argmax(logits + (long long)blockIdx.x * vocab, vocab, 1.f, scratch, &invalid);
     if (threadIdx.x == 0) out[blockIdx.x] = best.index;
 }
@@ -78,6 +79,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     __shared__ int invalid;
     __shared__ float sums[THREADS];
     __shared__ float reduce[32];
+    pdl_prologue();
     const int r = blockIdx.x;
     const float* row = logits + (long long)r * vocab;
     const Best best = block_argmax(row, vocab, 1.f, scratch, &invalid);
@@ -121,14 +123,12 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
 KIDI_API int kidi_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return KIDI_REFUSED_SIZE;
-    argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, out, vocab);
-    return kidi_launch_status();
+    return kidi_launch(argmax_kernel, rows, THREADS, 0, stream, logits, out, vocab);
 }
 
 KIDI_API int kidi_sample(const float* logits, int* out, int rows, int vocab, const float* temperature,
                          unsigned long long seed, const long long* keys, const int* steps, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return KIDI_REFUSED_SIZE;
-    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, out, vocab, temperature, seed, keys, steps);
-    return kidi_launch_status();
+    return kidi_launch(sample_kernel, rows, THREADS, 0, stream, logits, out, vocab, temperature, seed, keys, steps);
 }

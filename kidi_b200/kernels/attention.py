@@ -43,6 +43,7 @@ def library(head_dim: int) -> ctypes.CDLL:
         lib.kidi_attention_prefill.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_attention_decode.argtypes = [c_void_p, c_void_p]
         lib.kidi_attention_prefill.restype = lib.kidi_attention_decode.restype = c_int
+        ops.configure_library(lib)
         _libraries[head_dim] = lib
     return lib
 

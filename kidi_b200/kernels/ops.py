@@ -84,8 +84,18 @@ def core():
         for name in ("kidi_embedding", "kidi_add_rmsnorm", "kidi_silu_gate", "kidi_gemm_simt", "kidi_rope_store",
                      "kidi_attention_generic", "kidi_argmax", "kidi_sample", "kidi_advance_decode"):
             getattr(lib, name).restype = c_int
+        configure_library(lib)
         _core = lib
     return _core
+
+
+def configure_library(lib) -> None:
+    """Settings every kernel library takes: KIDI_B200_PDL=1 launches kernels with
+    programmatic dependent launch (an experiment switch; off by default)."""
+    import os
+    lib.kidi_set_pdl.argtypes = [c_int]
+    lib.kidi_set_pdl.restype = None
+    lib.kidi_set_pdl(1 if os.environ.get("KIDI_B200_PDL", "0") == "1" else 0)
 
 
 # ----------------------------------------------------------------- structures
