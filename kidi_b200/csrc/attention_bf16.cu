@@ -18,6 +18,7 @@
 // src/kidi/runtime/vulkan/attention.comp:32-101; causal rule
 // src/kidi/model/gemma4.cpp:736-740.
 #include "common.cuh"
+#include "attention_no_alloc.h"
 
 KIDI_DEFINE_PDL_FLAG()
 
@@ -501,4 +502,37 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
     if (status || a.splits == 1) return status;
     dim3 combine(a.heads, a.rows);
     return kidi_launch(attention_combine_kernel, combine, D >= 128 ? 128 : 64, 0, stream, a);
+}
+
+// ---------------------------------------------------------------------------
+// The variant that allocates nothing (attention_no_alloc.h). Its workspace is this
+// array; the host code below never uses the array's name as an address: it asks the
+// runtime for the device address once per device and passes that to the kernels.
+static __device__ __align__(256) float kidi_static_scratch[KIDI_STATIC_SCRATCH_FLOATS];
+
+KIDI_API long long kidi_attention_decode_static_need(int rows, int heads, int splits) {
+    return splits > 1 ? (long long)rows * heads * splits * (D + 2) : 0;
+}
+
+KIDI_API int kidi_attention_decode_static(const KidiAttentionArgs* args, cudaStream_t stream) {
+    constexpr int MAX_DEVICES = 64;
+    static float* scratch_of_device[MAX_DEVICES] = {nullptr};
+    Args a = *reinterpret_cast<const Args*>(args);
+    if (a.rows <= 0) return 0;
+    if (a.splits < 1 || a.heads <= 0) return KIDI_REFUSED_SIZE;
+    const long long need = kidi_attention_decode_static_need(a.rows, a.heads, a.splits);
+    if (need > KIDI_STATIC_SCRATCH_FLOATS) return KIDI_REFUSED_SIZE;  // more splits than the fixed workspace holds
+    int device = -1;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return (int)status;
+    if (device < 0 || device >= MAX_DEVICES) return KIDI_REFUSED_SIZE;
+    if (!scratch_of_device[device]) {  // set-up, once per device, with that device current
+        float* address = nullptr;
+        status = cudaGetSymbolAddress((void**)&address, kidi_static_scratch);
+        if (status != cudaSuccess) return (int)status;
+        scratch_of_device[device] = address;
+    }
+    a.partial_out = scratch_of_device[device];
+    a.partial_stat = scratch_of_device[device] + (long long)a.rows * a.heads * a.splits * D;
+    return kidi_attention_decode(&a, stream);
 }
