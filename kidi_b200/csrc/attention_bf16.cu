@@ -430,6 +430,248 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
     }
 }
 
+// The same for at most eight query heads per key/value head, in the transposed form that
+// needs half the tensor-core instructions and half the accumulator registers: the keys
+// are the rows of the score tile, S^T = K Q^T (16 keys x 8 heads per warp), and the
+// output is accumulated transposed, O^T = V^T P^T (head_dim x 8 heads). P^T reaches the
+// layout of a B operand through two 8x8 register transposes (movmatrix).
+__device__ int kidi_attention_timeout = 0;  // set when a bounded wait for a tile ran out
+
+__device__ __forceinline__ void bulk_copy_row(void* shared, const void* global, unsigned bytes,
+                                              unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_address(shared)),
+                 "l"(global), "r"(bytes), "r"(smem_address(bar))
+                 : "memory");
+}
+
+// One 64-row tile of keys and one of values, a bulk copy per row (rows are contiguous in
+// the cache and padded in shared memory): threads 0..63 bring key rows, 64..127 value
+// rows, thread 0 tells the barrier how many bytes to expect. Rows beyond `rows_valid`
+// are left as they are (zeros, or an earlier tile's finite values; their scores are masked).
+__device__ __forceinline__ void issue_tile(bf16* k_tile, bf16* v_tile, const bf16* k_cache, const bf16* v_cache,
+                                           const CacheGeometry& geometry, int slot, int kv_head, int tile,
+                                           int rows_valid, unsigned long long* bar) {
+    const long long page = cache_row_offset(geometry, slot, tile * TILE, kv_head);
+    const int r = threadIdx.x & 63;
+    if (threadIdx.x == 0)
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(bar)),
+                     "r"((unsigned)(rows_valid * D * 2 * 2))
+                     : "memory");
+    if (r < rows_valid) {
+        if (threadIdx.x < 64) bulk_copy_row(k_tile + r * PITCH, k_cache + page + (long long)r * D, D * 2, bar);
+        else bulk_copy_row(v_tile + r * PITCH, v_cache + page + (long long)r * D, D * 2, bar);
+    }
+}
+
+__device__ __forceinline__ void wait_tile(unsigned long long* bar, unsigned parity) {
+    for (unsigned spin = 0; spin < (1u << 24); ++spin) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(smem_address(bar)), "r"(parity)
+            : "memory");
+        if (done) return;
+    }
+    kidi_attention_timeout = 1;
+}
+
+__device__ __forceinline__ unsigned transpose_8x8(unsigned packed) {
+    unsigned out;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(out) : "r"(packed));
+    return out;
+}
+
+__global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    bf16* q_tile = reinterpret_cast<bf16*>(raw);            // [8][PITCH] (16 rows reserved)
+    bf16* k_tiles = q_tile + 16 * PITCH;                    // [2][64][PITCH]
+    bf16* v_tiles = k_tiles + 2 * TILE * PITCH;             // [2][64][PITCH]
+    pdl_prologue();
+    const int split = blockIdx.x, kv_head = blockIdx.y, row = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int matrix = lane >> 3, within = lane & 7;
+    const int group = a.heads / a.kv_heads;                 // <= 8
+    const int seq = a.row_seq[row];
+    const int head0 = kv_head * group;
+    // Lane (g, t) keeps heads 2t and 2t+1: running maximum, its own share of the
+    // denominator, and O^T[dims g / g+8 of each 16-dim tile][heads 2t, 2t+1].
+    float best[2] = {-INFINITY, -INFINITY}, denom[2] = {0.f, 0.f};
+    float o[D / 16][4];
+#pragma unroll
+    for (int n = 0; n < D / 16; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+
+    int tiles = 0, tile_first = 0, position = 0, low = 0, slot = 0;
+    if (seq >= 0) {
+        position = a.row_pos[row];
+        slot = a.seq_slot[seq];
+        low = a.window > 0 ? max(0, position - a.window + 1) : 0;
+        const int tile_low = low / TILE, tile_high = position / TILE;
+        const int all = tile_high - tile_low + 1;
+        const int per_split = (all + a.splits - 1) / a.splits;
+        tile_first = tile_low + split * per_split;
+        tiles = max(0, min(per_split, tile_high + 1 - tile_first));
+    }
+    __shared__ unsigned long long tile_bar[2];
+    if (tiles > 0) {
+        if (threadIdx.x == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&tile_bar[0])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&tile_bar[1])));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        // The tiles start as zeros: rows that no copy ever writes must be finite.
+        for (int chunk = threadIdx.x; chunk < 4 * TILE * PITCH / 8; chunk += THREADS)
+            reinterpret_cast<uint4*>(k_tiles)[chunk] = make_uint4(0u, 0u, 0u, 0u);
+        for (int chunk = threadIdx.x; chunk < 8 * CHUNKS; chunk += THREADS) {
+            const int r = chunk / CHUNKS, c = chunk - r * CHUNKS;
+            const bool valid = r < group;
+            const bf16* source = a.q + (long long)row * a.ldq + (long long)(head0 + (valid ? r : 0)) * D + c * 8;
+            copy_async_16(q_tile + r * PITCH + c * 8, source, valid);
+        }
+        copy_async_commit();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        issue_tile(k_tiles, v_tiles, a.k_cache, a.v_cache, a.cache, slot, kv_head, tile_first,
+                   min(TILE, position - tile_first * TILE + 1), &tile_bar[0]);
+        const float scale_log2 = a.scale * LOG2E;
+        unsigned q_frag[D / 16][2];                         // Q^T as B operand: (dims, head g)
+        for (int index = 0; index < tiles; ++index) {
+            const int tile = tile_first + index, buffer = index & 1;
+            if (index + 1 < tiles)                          // the other buffer was read in the step before
+                issue_tile(k_tiles + (buffer ^ 1) * TILE * PITCH, v_tiles + (buffer ^ 1) * TILE * PITCH, a.k_cache,
+                           a.v_cache, a.cache, slot, kv_head, tile + 1, min(TILE, position - (tile + 1) * TILE + 1),
+                           &tile_bar[buffer ^ 1]);
+            wait_tile(&tile_bar[buffer], (index >> 1) & 1);
+            if (index == 0) {
+                copy_async_wait<0>();
+                __syncthreads();
+#pragma unroll
+                for (int kk = 0; kk < D / 32; ++kk) {       // two 16-dim steps per load
+                    unsigned r4[4];
+                    ldmatrix_x4(r4, q_tile + within * PITCH + kk * 32 + matrix * 8);
+                    q_frag[2 * kk][0] = r4[0]; q_frag[2 * kk][1] = r4[1];
+                    q_frag[2 * kk + 1][0] = r4[2]; q_frag[2 * kk + 1][1] = r4[3];
+                }
+                if (D % 32) {                                // an odd number of 16-dim steps: the last one alone
+                    unsigned r4[4];
+                    ldmatrix_x4(r4, q_tile + within * PITCH + (D / 32) * 32 + (matrix & 1) * 8);
+                    q_frag[D / 16 - 1][0] = r4[0]; q_frag[D / 16 - 1][1] = r4[1];
+                }
+            }
+            const int first_key = warp * 16;
+            const bf16* k_tile = k_tiles + buffer * TILE * PITCH;
+            const bf16* v_tile = v_tiles + buffer * TILE * PITCH;
+            if (tile * TILE + first_key <= position && tile * TILE + first_key + 15 >= low) {
+                float s[4] = {0.f, 0.f, 0.f, 0.f};          // keys g (0,1) and g+8 (2,3) x heads 2t, 2t+1
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    unsigned k_frag[4];
+                    ldmatrix_x4(k_frag, k_tile + (first_key + within + (matrix & 1) * 8) * PITCH + kk * 16 + (matrix >> 1) * 8);
+                    mma_bf16(s, k_frag, q_frag[kk][0], q_frag[kk][1]);
+                }
+                const int u0 = tile * TILE + first_key + g, u1 = u0 + 8;
+                const bool see0 = u0 <= position && u0 >= low, see1 = u1 <= position && u1 >= low;
+                s[0] = see0 ? s[0] * scale_log2 : -INFINITY;
+                s[1] = see0 ? s[1] * scale_log2 : -INFINITY;
+                s[2] = see1 ? s[2] * scale_log2 : -INFINITY;
+                s[3] = see1 ? s[3] * scale_log2 : -INFINITY;
+                float top[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {               // over the eight lanes that share t
+                    top[i] = fmaxf(top[i], __shfl_xor_sync(0xffffffffu, top[i], 4));
+                    top[i] = fmaxf(top[i], __shfl_xor_sync(0xffffffffu, top[i], 8));
+                    top[i] = fmaxf(top[i], __shfl_xor_sync(0xffffffffu, top[i], 16));
+                }
+                float keep[2], use[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const float next = fmaxf(best[i], top[i]);
+                    use[i] = next == -INFINITY ? 0.f : next;
+                    keep[i] = exp2f(best[i] - use[i]);
+                    best[i] = next;
+                }
+                s[0] = exp2f(s[0] - use[0]);
+                s[1] = exp2f(s[1] - use[1]);
+                s[2] = exp2f(s[2] - use[0]);
+                s[3] = exp2f(s[3] - use[1]);
+                denom[0] = denom[0] * keep[0] + s[0] + s[2];
+                denom[1] = denom[1] * keep[1] + s[1] + s[3];
+#pragma unroll
+                for (int n = 0; n < D / 16; ++n) {
+                    o[n][0] *= keep[0]; o[n][1] *= keep[1]; o[n][2] *= keep[0]; o[n][3] *= keep[1];
+                }
+                const unsigned p0 = transpose_8x8(pack_bf16(s[0], s[1]));   // keys 2t, 2t+1 of head g
+                const unsigned p1 = transpose_8x8(pack_bf16(s[2], s[3]));   // keys 2t+8, 2t+9
+#pragma unroll
+                for (int n = 0; n < D / 16; ++n) {          // V^T as A operand: 16 dims x 16 keys
+                    unsigned v_frag[4];
+                    ldmatrix_x4_trans(v_frag, v_tile + (first_key + within + (matrix >> 1) * 8) * PITCH + n * 16 + (matrix & 1) * 8);
+                    mma_bf16(o[n], v_frag, p0, p1);
+                }
+            }
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {                           // the lanes' shares of the denominator
+        denom[i] += __shfl_xor_sync(0xffffffffu, denom[i], 4);
+        denom[i] += __shfl_xor_sync(0xffffffffu, denom[i], 8);
+        denom[i] += __shfl_xor_sync(0xffffffffu, denom[i], 16);
+    }
+
+    // Merge the four warps in warp order through shared memory (the tiles are free now).
+    float* merge_out = reinterpret_cast<float*>(k_tiles);                // [4][8][D]
+    float* merge_stat = merge_out + 4 * 8 * D;                           // [4][8][2]
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < D / 16; ++n) {
+        merge_out[(warp * 8 + 2 * t) * D + n * 16 + g] = o[n][0];
+        merge_out[(warp * 8 + 2 * t + 1) * D + n * 16 + g] = o[n][1];
+        merge_out[(warp * 8 + 2 * t) * D + n * 16 + g + 8] = o[n][2];
+        merge_out[(warp * 8 + 2 * t + 1) * D + n * 16 + g + 8] = o[n][3];
+    }
+    if (g == 0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            merge_stat[(warp * 8 + 2 * t + i) * 2] = best[i];
+            merge_stat[(warp * 8 + 2 * t + i) * 2 + 1] = denom[i];
+        }
+    }
+    __syncthreads();
+    for (int item = threadIdx.x; item < group * D; item += THREADS) {
+        const int r = item / D, c = item - r * D;
+        float top = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) top = fmaxf(top, merge_stat[(w * 8 + r) * 2]);
+        float total = 0.f, value = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float m = merge_stat[(w * 8 + r) * 2];
+            const float factor = m == -INFINITY ? 0.f : exp2f(m - top);
+            total += merge_stat[(w * 8 + r) * 2 + 1] * factor;
+            value += merge_out[(w * 8 + r) * D + c] * factor;
+        }
+        const int head = head0 + r;
+        if (a.splits == 1) {
+            a.out[(long long)row * a.ldo + (long long)head * D + c] =
+                from_float<bf16>(total > 0.f ? value / total : 0.f);
+        } else {
+            const long long where = ((long long)row * a.heads + head) * a.splits + split;
+            a.partial_out[where * D + c] = value;
+            if (c == 0) {
+                a.partial_stat[where * 2] = top;
+                a.partial_stat[where * 2 + 1] = total;
+            }
+        }
+    }
+}
+
 // grid (heads, rows): merges the splits of one (row, head) in split order.
 __global__ void attention_combine_kernel(Args a) {
     pdl_prologue();
@@ -494,11 +736,15 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   (int)DECODE_SHARED);
+        if (status == cudaSuccess)
+            status = cudaFuncSetAttribute(attention_decode_narrow_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)DECODE_SHARED);
         if (status != cudaSuccess) return (int)status;
         configured = true;
     }
     dim3 grid(a.splits, a.kv_heads, a.rows);
-    int status = kidi_launch(attention_decode_kernel, grid, THREADS, DECODE_SHARED, stream, a);
+    int status = group <= 8 ? kidi_launch(attention_decode_narrow_kernel, grid, THREADS, DECODE_SHARED, stream, a)
+                            : kidi_launch(attention_decode_kernel, grid, THREADS, DECODE_SHARED, stream, a);
     if (status || a.splits == 1) return status;
     dim3 combine(a.heads, a.rows);
     return kidi_launch(attention_combine_kernel, combine, D >= 128 ? 128 : 64, 0, stream, a);

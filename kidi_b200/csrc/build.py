@@ -39,7 +39,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-
 
 # The libraries of the package: name -> sources. Definitions are added per request.
 LIBRARIES: Dict[str, Tuple[str, ...]] = {
-    "core": ("elementwise.cu", "gemm_simt.cu", "gemm_skinny.cu", "attention_generic.cu", "sampling.cu"),
+    "core": ("elementwise.cu", "gemm_simt.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "attention_generic.cu",
+             "sampling.cu"),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -17,6 +17,7 @@ never read.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -138,8 +139,19 @@ class DecodeSession:
         torch.cuda.synchronize(self.engine.device)
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
-        with torch.cuda.graph(self.graph, stream=self._stream):
-            self._forward()
+        # Nothing but the step's own launches may touch CUDA while it is captured. The
+        # collector is held off (a finaliser of an unrelated object that frees device or
+        # pinned memory in the middle of the capture would invalidate it), and the capture
+        # is thread-local, as the reference's is (src/kidi/runtime/cuda/operators.cpp:262-276).
+        was_enabled = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, stream=self._stream, capture_error_mode="thread_local"):
+                self._forward()
+        finally:
+            if was_enabled:
+                gc.enable()
         self.kernels_per_step = ops.launch_count - before   # this package's kernels in one replay
         self.buffer.copy_(saved)
         torch.cuda.synchronize(self.engine.device)

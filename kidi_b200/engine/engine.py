@@ -51,12 +51,14 @@ class StepContext:
     def attention(self, qkv, out, **arguments) -> None:
         attention_kernels.run(self, qkv, out, **arguments)
 
-    def workspace(self, name: str, count: int) -> torch.Tensor:
-        """Scratch memory of at least `count` float32 elements that kernels of one
-        step may use one after another (it is kept between steps and grows on demand)."""
+    def workspace(self, name: str, count: int, zero: bool = False) -> torch.Tensor:
+        """Scratch memory of at least `count` 32-bit elements that kernels of one step may
+        use one after another (it is kept between steps and grows on demand). With `zero`
+        it is filled with zeros when it is made; its users leave it zero."""
         held = self._workspaces.get(name)
         if held is None or held.numel() < count:
-            held = torch.empty(max(count, 1), dtype=torch.float32, device=self.device)
+            make = torch.zeros if zero else torch.empty
+            held = make(max(count, 1), dtype=torch.float32, device=self.device)
             self._workspaces[name] = held
         return held
 

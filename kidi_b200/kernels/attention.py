@@ -61,12 +61,27 @@ def sm_count(device: torch.device) -> int:
     return _sm_count[index]
 
 
+BLOCKS_PER_SM = 3          # decode attention blocks that fit one SM (shared memory)
+FIXED_COST_TILES = 6.0     # what a block spends beside its tiles (launch, query, merge of splits), in tile times;
+                           # fitted to step times measured on a B200 at batch 1, 8 and 64
+
+
 def decode_splits(rows: int, kv_heads: int, longest: int, device: torch.device) -> int:
-    """How many blocks share a sequence's keys: enough to give every SM two blocks,
-    at most one per 64-key page."""
+    """How many blocks share a sequence's keys. A block walks its 64-key pages one after
+    another, so the kernel's time is (waves of blocks) x (pages per block + a fixed cost);
+    the number of splits that makes this smallest is chosen, at most one per page."""
     pages = max(1, -(-longest // 64))
-    wanted = -(-2 * sm_count(device) // max(1, rows * kv_heads))
-    return max(1, min(pages, wanted))
+    forced = int(os.environ.get("KIDI_B200_DECODE_SPLITS", "0"))
+    if forced:
+        return max(1, min(pages, forced))
+    slots = BLOCKS_PER_SM * sm_count(device)
+    items = max(1, rows * kv_heads)
+    best, best_cost = 1, None
+    for splits in range(1, min(pages, 32) + 1):
+        cost = -(-items * splits // slots) * (-(-pages // splits) + FIXED_COST_TILES)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = splits, cost
+    return best
 
 
 def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step) -> None:

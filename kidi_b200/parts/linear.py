@@ -6,8 +6,12 @@ registered part. Which kernel runs follows the element types:
 
 * a 32-bit input or a 32-bit weight: the 32-bit CUDA-core product (ascending-k fused
   multiply-adds; no reduced-precision matrix mode);
-* bfloat16 by bfloat16 with few rows (decode): the weight-streaming tensor-core
-  kernel of this package, when the shape fits it;
+* bfloat16 by bfloat16 with up to 8 rows (decode): the weight-streaming `mma.sync`
+  kernel of this package (`kernels/skinny.py`);
+* bfloat16 by bfloat16 with 9 to 64 rows and a large weight (16384 output features or
+  more: the fused gate/up projection, the output head): this package's tcgen05 kernel
+  (`kernels/tcgen05.py`: TMA-fed, accumulating in tensor memory), which streams such
+  weights as fast as the vendor library does;
 * bfloat16 by bfloat16 otherwise: the vendor matrix library through `torch.mm`, which
   is where the reference's CUDA engine calls a library too
   (docs/cuda-performance-plan.md:47-52).
@@ -34,9 +38,11 @@ class Linear:
         weight = self.weight
         if x.dtype == torch.float32 or weight.dtype == torch.float32:
             return ops.gemm_simt(x, weight, out_dtype, out=out)
-        from ..kernels import skinny
+        from ..kernels import skinny, tcgen05
         if skinny.fits(x, weight):
             return skinny.gemm(x, weight, out_dtype, out=out)
+        if weight.shape[0] >= tcgen05.MIN_FEATURES and tcgen05.fits(x, weight):
+            return tcgen05.gemm(x, weight, out_dtype, out=out)
         if weight.shape[1] % 8 or x.stride(0) % 8:  # the library wants 16-byte rows; keep odd widths exact
             return ops.gemm_simt(x, weight, out_dtype, out=out)
         if out is not None:

@@ -113,6 +113,41 @@ def test_gemm_skinny_silu_gate(rows):
     close(out, gate / (1 + torch.exp(-gate)) * up, 5e-3, "fused silu gate")
 
 
+@pytest.mark.parametrize("rows", [1, 8, 13, 40, 64, 100, 300])
+@pytest.mark.parametrize("shape", [(389, 96), (100, 200), (4096, 1024), (130, 4104)])
+@pytest.mark.parametrize("splits", [1, 3, None])
+def test_gemm_tcgen05(rows, shape, splits):
+    """The tensor-memory kernel: every tile size, ragged edges in all three dimensions,
+    with and without split-K (whose partial sums are added in slice order)."""
+    from kidi_b200.kernels import tcgen05
+    N, K = shape
+    generator = torch.Generator().manual_seed(rows * 1000 + N)
+    x = torch.randn(rows, K, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=generator) / math.sqrt(K)).to(torch.bfloat16)
+    expected = x.double() @ w.double().T
+    for out_dtype, tolerance in ((torch.float32, 2e-5), (torch.bfloat16, 5e-3)):
+        out = tcgen05.gemm(x.to(DEVICE), w.to(DEVICE), out_dtype, splits=splits)
+        close(out, expected, tolerance, f"gemm_tcgen05 {rows}x{N}x{K} splits {splits} -> {out_dtype}")
+        again = tcgen05.gemm(x.to(DEVICE), w.to(DEVICE), out_dtype, splits=splits)
+        assert torch.equal(out, again)          # the sum over slices does not depend on timing
+    assert tcgen05.error_code(torch.device(DEVICE)) == 0
+
+
+@pytest.mark.parametrize("rows", [1, 17, 64, 150])
+@pytest.mark.parametrize("splits", [1, 2])
+def test_gemm_tcgen05_silu_gate(rows, splits):
+    from kidi_b200.kernels import tcgen05
+    inter, K = 200, 96
+    generator = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, K, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, K, generator=generator) / math.sqrt(K) * 2).to(torch.bfloat16)
+    gate = x.double() @ w[:inter].double().T
+    up = x.double() @ w[inter:].double().T
+    out = tcgen05.gemm_silu_gate(x.to(DEVICE), w.to(DEVICE), splits=splits)
+    close(out, gate / (1 + torch.exp(-gate)) * up, 5e-3, "fused silu gate (tcgen05)")
+    assert tcgen05.error_code(torch.device(DEVICE)) == 0
+
+
 # ------------------------------------------------------ rope, cache, attention
 class Tables:
     pass
@@ -233,9 +268,9 @@ class FakeContext:
         self.decode_splits = splits
         self._held = {}
 
-    def workspace(self, name, count):
+    def workspace(self, name, count, zero=False):
         if name not in self._held or self._held[name].numel() < count:
-            self._held[name] = torch.empty(count, dtype=torch.float32, device=DEVICE)
+            self._held[name] = (torch.zeros if zero else torch.empty)(count, dtype=torch.float32, device=DEVICE)
         return self._held[name]
 
 
