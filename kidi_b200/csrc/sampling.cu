@@ -59,6 +59,41 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
     if (threadIdx.x == 0) out[blockIdx.x] = best.index;
 }
 
+// Greedy selection in two stages, so that a row's vocabulary is scanned by many blocks:
+// stage one reduces a slice of the row per block, stage two the slices of a row.
+// index -2 marks a slice that holds a NaN or +infinity.
+__global__ void __launch_bounds__(THREADS)
+argmax_slices_kernel(const float* __restrict__ logits, float* __restrict__ slice_value, int* __restrict__ slice_index,
+                     int vocab, int slices) {
+    __shared__ Best scratch[THREADS / 32];
+    __shared__ int invalid;
+    pdl_prologue();
+    const int slice = blockIdx.x, row = blockIdx.y;
+    const int width = (vocab + slices - 1) / slices;
+    const int begin = min(vocab, slice * width), count = min(vocab, begin + width) - begin;
+    Best best = block_argmax(logits + (long long)row * vocab + begin, count, 1.f, scratch, &invalid);
+    if (threadIdx.x == 0) {
+        const bool bad = invalid != 0;
+        slice_value[row * slices + slice] = best.value;
+        slice_index[row * slices + slice] = bad ? -2 : (best.index >= 0 ? best.index + begin : -1);
+    }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ slice_value, const int* __restrict__ slice_index,
+                                    int* __restrict__ out, int slices) {
+    pdl_prologue();
+    const int row = blockIdx.x;
+    if (threadIdx.x != 0) return;
+    Best best{-INFINITY, -1};
+    bool bad = false;
+    for (int s = 0; s < slices; ++s) {  // ascending slices: the first maximum stays
+        const int index = slice_index[row * slices + s];
+        bad |= index == -2;
+        if (index >= 0 && slice_value[row * slices + s] > best.value) best = Best{slice_value[row * slices + s], index};
+    }
+    out[row] = bad ? -1 : best.index;
+}
+
 // 64-bit mix (splitmix64 finaliser) of the three keys; 24 random bits -> u in [0, 1).
 __device__ __forceinline__ float uniform_from(unsigned long long seed, unsigned long long key,
                                               unsigned long long step) {
@@ -75,19 +110,16 @@ __device__ __forceinline__ float uniform_from(unsigned long long seed, unsigned 
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, const float* __restrict__ temperature,
               unsigned long long seed, const long long* __restrict__ keys, const int* __restrict__ steps) {
-    __shared__ Best scratch[THREADS / 32];
-    __shared__ int invalid;
     __shared__ float sums[THREADS];
     __shared__ float reduce[32];
     pdl_prologue();
     const int r = blockIdx.x;
     const float* row = logits + (long long)r * vocab;
-    const Best best = block_argmax(row, vocab, 1.f, scratch, &invalid);
+    // out[r] holds the row's argmax already (the two greedy stages ran before this kernel).
     const float t = temperature[r];
-    if (best.index < 0 || !(t > 0.f)) {  // greedy, or nothing to draw from
-        if (threadIdx.x == 0) out[r] = best.index;
-        return;
-    }
+    const int top = out[r];
+    if (top < 0 || !(t > 0.f)) return;  // greedy, or nothing to draw from
+    const Best best{row[top], top};
     const float inverse = 1.0f / t;
     const int chunk = (vocab + THREADS - 1) / THREADS;
     const int begin = min(vocab, (int)threadIdx.x * chunk), end = min(vocab, begin + chunk);
@@ -120,15 +152,28 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
 }
 }  // namespace
 
-KIDI_API int kidi_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+// The number of slices a row is cut into, and the floats of scratch a call needs
+// (rows * slices values, then rows * slices indices).
+KIDI_API int kidi_argmax_slices(int vocab) { return vocab >= 65536 ? 32 : vocab >= 8192 ? 8 : 1; }
+
+KIDI_API int kidi_argmax(const float* logits, int* out, int rows, int vocab, float* scratch, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (vocab <= 0) return KIDI_REFUSED_SIZE;
-    return kidi_launch(argmax_kernel, rows, THREADS, 0, stream, logits, out, vocab);
+    if (vocab <= 0 || rows > 65535) return KIDI_REFUSED_SIZE;
+    const int slices = kidi_argmax_slices(vocab);
+    if (slices == 1 || !scratch) return kidi_launch(argmax_kernel, rows, THREADS, 0, stream, logits, out, vocab);
+    float* values = scratch;
+    int* indices = reinterpret_cast<int*>(scratch + (long long)rows * slices);
+    int status = kidi_launch(argmax_slices_kernel, dim3(slices, rows), THREADS, 0, stream, logits, values, indices,
+                             vocab, slices);
+    if (status) return status;
+    return kidi_launch(argmax_merge_kernel, rows, 32, 0, stream, (const float*)values, (const int*)indices, out, slices);
 }
 
+// Greedy rows (temperature 0) are final after the argmax stages; the others are drawn.
 KIDI_API int kidi_sample(const float* logits, int* out, int rows, int vocab, const float* temperature,
-                         unsigned long long seed, const long long* keys, const int* steps, cudaStream_t stream) {
-    if (rows <= 0) return 0;
-    if (vocab <= 0) return KIDI_REFUSED_SIZE;
+                         unsigned long long seed, const long long* keys, const int* steps, float* scratch,
+                         cudaStream_t stream) {
+    int status = kidi_argmax(logits, out, rows, vocab, scratch, stream);
+    if (status || rows <= 0) return status;
     return kidi_launch(sample_kernel, rows, THREADS, 0, stream, logits, out, vocab, temperature, seed, keys, steps);
 }

@@ -76,9 +76,11 @@ def core():
                                        c_longlong, c_longlong, c_longlong, c_void_p]
         lib.kidi_rope_store.argtypes = [c_void_p, c_int, c_int, c_void_p]
         lib.kidi_attention_generic.argtypes = [c_void_p, c_int, c_void_p]
-        lib.kidi_argmax.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.kidi_argmax.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.kidi_sample.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_ulonglong, c_void_p, c_void_p,
-                                    c_void_p]
+                                    c_void_p, c_void_p]
+        lib.kidi_argmax_slices.argtypes = [c_int]
+        lib.kidi_argmax_slices.restype = c_int
         lib.kidi_advance_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_void_p]
         for name in ("kidi_embedding", "kidi_add_rmsnorm", "kidi_silu_gate", "kidi_gemm_simt", "kidi_rope_store",
@@ -268,8 +270,17 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     rows, vocab = logits.shape
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    _check(core().kidi_argmax(_ptr(logits), _ptr(out), rows, vocab, _stream()), "argmax")
+    scratch, launches = _argmax_scratch(rows, vocab, logits.device)
+    _check(core().kidi_argmax(_ptr(logits), _ptr(out), rows, vocab, _ptr(scratch), _stream()), "argmax", launches)
     return out
+
+
+def _argmax_scratch(rows: int, vocab: int, device):
+    """Scratch for the two-stage argmax of a wide vocabulary (None when one stage does)."""
+    slices = core().kidi_argmax_slices(vocab)
+    if slices == 1:
+        return None, 1
+    return torch.empty(2 * rows * slices, dtype=torch.float32, device=device), 2
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: int, keys: torch.Tensor, steps: torch.Tensor,
@@ -285,9 +296,10 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: int, keys: tor
         raise invalid_argument("sample: temperature float32, keys int64 and steps int32, one per row")
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    scratch, launches = _argmax_scratch(rows, vocab, logits.device)
     _check(core().kidi_sample(_ptr(logits), _ptr(out), rows, vocab, _ptr(temperature),
-                              ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _ptr(keys), _ptr(steps), _stream()),
-           "sample")
+                              ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _ptr(keys), _ptr(steps), _ptr(scratch),
+                              _stream()), "sample", launches + 1)
     return out
 
 

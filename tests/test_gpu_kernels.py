@@ -61,13 +61,14 @@ def test_add_rmsnorm(hidden, dtype):
     close(picked, plain_model.rms_norm(before.cpu().double()[rows.long()], weight.double(), eps), 1e-5, "picked rows")
 
 
-def test_silu_gate():
+@pytest.mark.parametrize("dtype,inter", [(torch.float32, 136), (torch.bfloat16, 136), (torch.bfloat16, 201)])
+def test_silu_gate(dtype, inter):
     from kidi_b200.kernels import ops
     generator = torch.Generator().manual_seed(1)
-    gate_up = torch.randn(5, 2 * 136, generator=generator) * 4
+    gate_up = (torch.randn(37, 2 * inter, generator=generator) * 4).to(dtype)
     out = ops.silu_gate(gate_up.to(DEVICE))
-    gate, up = gate_up[:, :136].double(), gate_up[:, 136:].double()
-    close(out, gate / (1 + torch.exp(-gate)) * up, 1e-6, "silu gate")
+    gate, up = gate_up[:, :inter].double(), gate_up[:, inter:].double()
+    close(out, gate / (1 + torch.exp(-gate)) * up, 1e-6 if dtype == torch.float32 else 5e-3, "silu gate")
 
 
 # ----------------------------------------------------------------------- gemm
@@ -446,6 +447,15 @@ def test_argmax_rules():
     found = ops.argmax(logits.to(DEVICE)).cpu().tolist()
     assert found == [17, -1, -1, -1, 999, int(logits[5].argmax())]
     assert found == [plain_model.greedy_token(row.numpy()) for row in logits]
+    # A wide vocabulary is scanned in slices by many blocks: the same rules across slice borders.
+    wide = torch.randn(6, 151936, generator=torch.Generator().manual_seed(3))
+    wide[0, 4747] = wide[0, 4748] = wide[0, 150000] = 50.0      # a tie across two slices
+    wide[1, 100000] = float("nan")
+    wide[2, 151935] = float("inf")
+    wide[3, :] = float("-inf")
+    wide[4, 151935] = 60.0
+    found = ops.argmax(wide.to(DEVICE)).cpu().tolist()
+    assert found == [4747, -1, -1, -1, 151935, int(wide[5].argmax())]
 
 
 @pytest.mark.parametrize("vocab", [389, 151936])
