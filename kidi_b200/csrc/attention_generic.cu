@@ -115,12 +115,103 @@ __global__ void __launch_bounds__(128) rope_store_kernel(RopeStoreArgs a) {
     }
 }
 
+// The same for bfloat16 rows in 16-byte vectors: lane l owns elements 8l..8l+7 of the head,
+// and its rotation partners are the eight elements of lane l +- half/8, fetched with
+// shuffles. Needs head_dim and rotary_dim/2 to be multiples of 8 and 16-byte aligned rows.
+template <typename TW>
+__global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a) {
+    pdl_prologue();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_heads = a.heads + 2 * a.kv_heads;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)a.rows * total_heads) return;
+    const int row = (int)(item / total_heads);
+    const int head = (int)(item - (long long)row * total_heads);
+    const int seq = a.row_seq[row];
+    if (seq < 0) return;
+    const int position = a.row_pos[row];
+    const int d = a.head_dim, c0 = 8 * lane;
+    const bool mine = c0 < d;
+    bf16* vector = (bf16*)a.qkv + row * a.ld + (long long)head * d;
+
+    bf16* cached = nullptr;
+    if (head >= a.heads && a.k_cache) {
+        bool keep = true;
+        if (a.cache.ring_pages) {
+            const int ring_tokens = a.cache.ring_pages << a.cache.page_shift;
+            keep = position >= a.seq_start[seq] + a.seq_len[seq] - ring_tokens;
+        }
+        if (keep) {
+            const bool is_key = head < a.heads + a.kv_heads;
+            const int kv_head = is_key ? head - a.heads : head - a.heads - a.kv_heads;
+            cached = (bf16*)(is_key ? a.k_cache : a.v_cache) +
+                     cache_row_offset(a.cache, a.seq_slot[seq], position, kv_head);
+        }
+    }
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (mine) raw = *reinterpret_cast<const uint4*>(vector + c0);
+    if (head >= a.heads + a.kv_heads || !a.transform) {  // a value head, or copy only
+        if (cached && mine) *reinterpret_cast<uint4*>(cached + c0) = raw;
+        return;
+    }
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float v[8];
+    float square = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 two = __bfloat1622float2(pairs[i]);
+        v[2 * i] = two.x;
+        v[2 * i + 1] = two.y;
+        square = fmaf(two.x, two.x, square);
+        square = fmaf(two.y, two.y, square);
+    }
+    const TW* weight = (const TW*)(head < a.heads ? a.q_norm : a.k_norm);
+    if (weight) {
+        const float inv = 1.0f / sqrtf(warp_sum(square) / (float)d + a.eps);
+        if (mine)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * to_float(weight[c0 + i]);
+    }
+    if (a.cos_table) {
+        const int half = a.rotary_dim / 2;
+        const bool low = c0 < half;
+        const int partner = low ? lane + half / 8 : lane - half / 8;
+        float other[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) other[i] = __shfl_sync(0xffffffffu, v[i], partner & 31);
+        if (mine && c0 < a.rotary_dim) {
+            const int j = low ? c0 : c0 - half;
+            const float4* cosine = reinterpret_cast<const float4*>(a.cos_table + (long long)position * half + j);
+            const float4* sine = reinterpret_cast<const float4*>(a.sin_table + (long long)position * half + j);
+            const float4 ca = cosine[0], cb = cosine[1], sa = sine[0], sb = sine[1];
+            const float c8[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+            const float s8[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = v[i] * c8[i] + (low ? -other[i] : other[i]) * s8[i];
+        }
+    }
+    if (mine) {
+        uint4 packed;
+        __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(vector + c0) = packed;
+        if (cached) *reinterpret_cast<uint4*>(cached + c0) = packed;
+    }
+}
+
 KIDI_API int kidi_rope_store(const RopeStoreArgs* args, int dtype, int norm_dtype, cudaStream_t stream) {
     const RopeStoreArgs& a = *args;
     if (a.rows <= 0) return 0;
     if (a.head_dim > 256 || a.head_dim <= 0 || a.rotary_dim > a.head_dim || (a.rotary_dim & 1)) return KIDI_REFUSED_SIZE;
     const long long items = (long long)a.rows * (a.heads + 2 * a.kv_heads);
     const unsigned blocks = (unsigned)((items + 3) / 4);
+    const bool vectors = dtype == KIDI_BF16 && !(a.head_dim & 7) && !(a.ld & 7) && !((uintptr_t)a.qkv & 15) &&
+                         !((uintptr_t)a.k_cache & 15) && !((uintptr_t)a.v_cache & 15) &&
+                         (!a.cos_table || (!(a.rotary_dim & 15) && !((uintptr_t)a.cos_table & 15) &&
+                                           !((uintptr_t)a.sin_table & 15)));
+    if (vectors && norm_dtype == KIDI_F32) return kidi_launch(rope_store_bf16_kernel<float>, blocks, 128, 0, stream, a);
+    if (vectors && norm_dtype == KIDI_BF16) return kidi_launch(rope_store_bf16_kernel<bf16>, blocks, 128, 0, stream, a);
     if (dtype == KIDI_F32 && norm_dtype == KIDI_F32) return kidi_launch(rope_store_kernel<float, float>, blocks, 128, 0, stream, a);
     if (dtype == KIDI_F32 && norm_dtype == KIDI_BF16) return kidi_launch(rope_store_kernel<float, bf16>, blocks, 128, 0, stream, a);
     if (dtype == KIDI_BF16 && norm_dtype == KIDI_F32) return kidi_launch(rope_store_kernel<bf16, float>, blocks, 128, 0, stream, a);
