@@ -91,6 +91,7 @@ struct Args {
     float* partial_out;   // [rows, heads, splits, D]
     float* partial_stat;  // [rows, heads, splits, 2]  (maximum in log2 units, denominator)
     int splits;
+    int* counters;        // [rows, kv_heads], zero between calls: the last block of a (row, kv head) merges its splits
 };
 
 // Loads one 64 x D tile of keys (or values) for absolute key positions [tile*64, tile*64+64)
@@ -670,6 +671,61 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
             }
         }
     }
+    if (a.splits > 1 && a.counters) {
+        // The block that finishes last for this (row, key/value head) merges the splits: in
+        // split order whichever block it is, so the result does not depend on timing. All the
+        // partial maxima and denominators are fetched at once, then every thread adds the
+        // partial outputs of its elements with the loads of a few splits in flight together.
+        __shared__ int last_block;
+        float* stat_max = merge_stat;                  // [group][splits]
+        float* stat_factor = merge_stat + 8 * 32;      // [group][splits]; then [group] 1 / denominator
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0)
+            last_block = atomicAdd(a.counters + (long long)row * a.kv_heads + kv_head, 1) == a.splits - 1;
+        __syncthreads();
+        if (!last_block) return;
+        __threadfence();
+        const int splits = a.splits;                   // <= 32
+        for (int i = threadIdx.x; i < group * splits; i += THREADS) {
+            const int r = i / splits, sp = i - r * splits;
+            const long long where = ((long long)row * a.heads + head0 + r) * splits + sp;
+            stat_max[r * 32 + sp] = __ldcg(a.partial_stat + where * 2);
+            stat_factor[r * 32 + sp] = __ldcg(a.partial_stat + where * 2 + 1);
+        }
+        __syncthreads();
+        if (threadIdx.x < group) {
+            const int r = threadIdx.x;
+            float top = -INFINITY, total = 0.f;
+            for (int sp = 0; sp < splits; ++sp) top = fmaxf(top, stat_max[r * 32 + sp]);
+            for (int sp = 0; sp < splits; ++sp) {
+                const float m = stat_max[r * 32 + sp];
+                const float factor = m == -INFINITY ? 0.f : exp2f(m - top);
+                total += stat_factor[r * 32 + sp] * factor;
+                stat_factor[r * 32 + sp] = factor;
+            }
+            stat_factor[8 * 32 + r] = total > 0.f ? 1.0f / total : 0.f;
+        }
+        __syncthreads();
+        for (int item = threadIdx.x; item < group * D; item += THREADS) {
+            const int r = item / D, c = item - r * D;
+            const int head = head0 + r;
+            const float* part = a.partial_out + ((long long)row * a.heads + head) * splits * D + c;
+            float value = 0.f;
+            int sp = 0;
+            for (; sp + 4 <= splits; sp += 4) {
+                const float v0 = __ldcg(part + (long long)sp * D), v1 = __ldcg(part + (long long)(sp + 1) * D);
+                const float v2 = __ldcg(part + (long long)(sp + 2) * D), v3 = __ldcg(part + (long long)(sp + 3) * D);
+                value += v0 * stat_factor[r * 32 + sp];
+                value += v1 * stat_factor[r * 32 + sp + 1];
+                value += v2 * stat_factor[r * 32 + sp + 2];
+                value += v3 * stat_factor[r * 32 + sp + 3];
+            }
+            for (; sp < splits; ++sp) value += __ldcg(part + (long long)sp * D) * stat_factor[r * 32 + sp];
+            a.out[(long long)row * a.ldo + (long long)head * D + c] = from_float<bf16>(value * stat_factor[8 * 32 + r]);
+        }
+        if (threadIdx.x == 0) a.counters[(long long)row * a.kv_heads + kv_head] = 0;
+    }
 }
 
 // grid (heads, rows): merges the splits of one (row, head) in split order.
@@ -693,7 +749,7 @@ __global__ void attention_combine_kernel(Args a) {
 
 constexpr size_t PREFILL_SHARED = (size_t)(TILE + 4 * TILE) * PITCH * sizeof(bf16);
 constexpr size_t DECODE_TILES = (size_t)(16 + 4 * TILE) * PITCH * sizeof(bf16);
-constexpr size_t DECODE_MERGE = (size_t)16 * PITCH * sizeof(bf16) + (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
+constexpr size_t DECODE_MERGE = (size_t)16 * PITCH * sizeof(bf16) + (size_t)(4 * 16 * D + 4 * 16 * 2 + 2 * 8 * 32 + 8) * sizeof(float);
 constexpr size_t DECODE_SHARED = DECODE_TILES > DECODE_MERGE ? DECODE_TILES : DECODE_MERGE;
 
 bool aligned(const Args& a) {
@@ -730,7 +786,8 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
     if (a.rows <= 0) return 0;
     const int group = a.kv_heads > 0 ? a.heads / a.kv_heads : 0;
     if (a.cache.head_dim != D || a.heads % a.kv_heads || group > 16 || a.kv_heads > 65535 || a.rows > 65535 ||
-        !aligned(a) || a.cache.page_shift != 6 || a.splits < 1 || (a.splits > 1 && (!a.partial_out || !a.partial_stat)))
+        !aligned(a) || a.cache.page_shift != 6 || a.splits < 1 || (a.splits > 1 && (!a.partial_out || !a.partial_stat)) ||
+        (a.counters && a.splits > 32))
         return KIDI_REFUSED_SIZE;
     static bool configured = false;
     if (!configured) {
@@ -745,7 +802,7 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
     dim3 grid(a.splits, a.kv_heads, a.rows);
     int status = group <= 8 ? kidi_launch(attention_decode_narrow_kernel, grid, THREADS, DECODE_SHARED, stream, a)
                             : kidi_launch(attention_decode_kernel, grid, THREADS, DECODE_SHARED, stream, a);
-    if (status || a.splits == 1) return status;
+    if (status || a.splits == 1 || (group <= 8 && a.counters)) return status;
     dim3 combine(a.heads, a.rows);
     return kidi_launch(attention_combine_kernel, combine, D >= 128 ? 128 : 64, 0, stream, a);
 }
@@ -780,5 +837,6 @@ KIDI_API int kidi_attention_decode_static(const KidiAttentionArgs* args, cudaStr
     }
     a.partial_out = scratch_of_device[device];
     a.partial_stat = scratch_of_device[device] + (long long)a.rows * a.heads * a.splits * D;
+    a.counters = nullptr;  // the splits are merged by the second kernel
     return kidi_attention_decode(&a, stream);
 }

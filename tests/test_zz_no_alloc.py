@@ -43,7 +43,7 @@ def make_case(rows, heads, kv_heads, head_dim, lengths, seed):
             tables["seq_start"].data_ptr(), tables["seq_len"].data_ptr(), tables["seq_row0"].data_ptr(),
             rows, rows, heads, kv_heads, 0, 1.0 / math.sqrt(head_dim),
             workspace.data_ptr() if workspace is not None else 0,
-            workspace.data_ptr() + count * head_dim * 4 if workspace is not None else 0, splits)
+            workspace.data_ptr() + count * head_dim * 4 if workspace is not None else 0, splits, 0)
 
     return arguments, (cache, tables, qkv)
 
