@@ -22,7 +22,7 @@ It prints ONE line of JSON:
 Every decode step reads about 16 GB of weights and cache, far more than the 126 MB L2, so
 no L2 flush is needed between timed steps. Peaks come from MEASURED_PEAKS.json beside
 this file when the driver wrote it. The reference arm cannot run here: the reference
-does not build without its third-party submodules.
+does not build without its third-party submodules, which are empty in the mounted tree.
 """
 import argparse
 import json
