@@ -761,6 +761,13 @@ bool aligned(const Args& a) {
 
 KIDI_API int kidi_attention_head_dim() { return D; }
 
+// Whether a bounded wait for a tile ever ran out in this process (reads the flag back; synchronises).
+KIDI_API int kidi_attention_timeout_flag() {
+    int flag = 0;
+    if (cudaMemcpyFromSymbol(&flag, kidi_attention_timeout, sizeof(int)) != cudaSuccess) return -1;
+    return flag;
+}
+
 // max_new: the longest seq_len of the step (sizes the grid).
 KIDI_API int kidi_attention_prefill(const Args* args, int max_new, cudaStream_t stream) {
     const Args& a = *args;

@@ -181,7 +181,17 @@ class Engine:
                 backend = self._backends[key] = EngineBackend(self, Sampler(seed), use_graph)
             found = generate(backend, prompts, options, stop_ids=self.spec.eos_token_ids, max_tokens=max_tokens,
                              stats=stats)
+            self.check_device_errors()
         return found if detailed else [generation.token_ids for generation in found]
+
+    def check_device_errors(self) -> None:
+        """Raises if a kernel gave up a bounded wait (its result would be wrong). Kernels
+        that wait on barriers record that instead of hanging; this reads the records."""
+        from ..kernels import tcgen05
+        code = tcgen05.error_code(self.device)
+        if code or attention_kernels.timeout_flags():
+            raise runtime_error(f"a kernel gave up waiting for its data (matrix product code {code}); "
+                                f"the results of this engine cannot be trusted")
 
     # ------------------------------------------------------------- accounting
     def memory(self) -> Dict[str, int]:

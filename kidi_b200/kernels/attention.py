@@ -21,6 +21,8 @@ from .ops import CacheGeometry, _check, c_float, c_int, c_longlong, c_void_p, ca
 
 FORCE_GENERIC = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1"
 FUSED_MERGE = os.environ.get("KIDI_B200_FUSED_MERGE", "1") == "1"
+TENSOR_MEMORY_PREFILL = os.environ.get("KIDI_B200_TCGEN05_ATTENTION", "1") == "1"
+TENSOR_MEMORY_HEAD_DIMS = (64, 128)
 
 
 class FastAttentionArgs(ctypes.Structure):
@@ -34,6 +36,7 @@ class FastAttentionArgs(ctypes.Structure):
 
 
 _libraries: Dict[int, ctypes.CDLL] = {}
+_tensor_memory_libraries: Dict[int, ctypes.CDLL] = {}
 _sm_count: Dict[int, int] = {}
 
 
@@ -48,6 +51,52 @@ def library(head_dim: int) -> ctypes.CDLL:
         ops.configure_library(lib)
         _libraries[head_dim] = lib
     return lib
+
+
+def tensor_memory_library(head_dim: int) -> ctypes.CDLL:
+    """The tcgen05 prompt-attention kernel compiled for one head width (64 or 128)."""
+    lib = _tensor_memory_libraries.get(head_dim)
+    if lib is None:
+        lib = load_library(f"attention_tcgen05_d{head_dim}", ("attention_tcgen05.cu",), {"KIDI_HEAD_DIM": head_dim})
+        lib.kidi_attention_prefill_tcgen05.argtypes = [
+            c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+            c_float, c_void_p]
+        lib.kidi_attention_prefill_tcgen05.restype = c_int
+        lib.kidi_attention_tcgen05_timeout_flag.restype = c_int
+        ops.configure_library(lib)
+        _tensor_memory_libraries[head_dim] = lib
+    return lib
+
+
+def tensor_memory_fits(qkv: torch.Tensor, out: torch.Tensor, head_dim: int, heads: int, kv_heads: int,
+                       scale: float = 1.0) -> bool:
+    """Prompts whose keys are all rows of the step, in bfloat16 with 16-byte aligned rows."""
+    return (TENSOR_MEMORY_PREFILL and scale > 0 and not FORCE_GENERIC and head_dim in TENSOR_MEMORY_HEAD_DIMS
+            and qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and heads % kv_heads == 0
+            and qkv.stride(1) == 1 and out.stride(1) == 1 and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+            and qkv.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
+def prefill_tensor_memory(qkv: torch.Tensor, out: torch.Tensor, seq_len: torch.Tensor, seq_row0: torch.Tensor,
+                          seqs: int, max_new: int, *, heads: int, kv_heads: int, head_dim: int, scale: float,
+                          window: int) -> None:
+    """Causal attention of packed prompts that start at position 0 (every key is a row of qkv)."""
+    lib = tensor_memory_library(head_dim)
+    _check(lib.kidi_attention_prefill_tcgen05(
+        qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), out.stride(0), seq_len.data_ptr(),
+        seq_row0.data_ptr(), seqs, max_new, heads, kv_heads, int(window or 0), float(scale), ops._stream()),
+        "attention_prefill_tcgen05")
+
+
+def timeout_flags() -> int:
+    """Non-zero when a bounded wait in one of the loaded attention libraries ran out."""
+    found = 0
+    for lib in _libraries.values():
+        lib.kidi_attention_timeout_flag.restype = c_int
+        found |= int(lib.kidi_attention_timeout_flag() != 0)
+    for lib in _tensor_memory_libraries.values():
+        found |= int(lib.kidi_attention_tcgen05_timeout_flag() != 0)
+    return found
 
 
 def fast_fits(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, decode: bool) -> bool:
@@ -92,6 +141,11 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
     if not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode) or (kv_view is not None and kv_view.page_size != 64):
         ops.attention_generic(qkv, out, heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale,
                               window=window, tables=tables, kv_view=kv_view, keys_in_step=keys_in_step)
+        return
+    if (not decode and keys_in_step and int(plan.seq_start.max()) == 0
+            and tensor_memory_fits(qkv, out, head_dim, heads, kv_heads, scale)):
+        prefill_tensor_memory(qkv, out, tables.seq_len, tables.seq_row0, plan.n_seqs, plan.max_new, heads=heads,
+                              kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
         return
     item = qkv.element_size()
     args = FastAttentionArgs(

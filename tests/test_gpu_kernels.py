@@ -412,6 +412,57 @@ def test_attention_decode(kind, dtype, geometry, splits):
         close(out[index:index + 1], expected, tolerance, f"{kind}: sequence of {start + 1} tokens, {splits} splits")
 
 
+@pytest.mark.parametrize("geometry", [(8, 2, 128, None), (4, 4, 64, None), (6, 1, 128, 200), (2, 2, 64, 130),
+                                      (5, 5, 128, 64)])
+def test_attention_prompts_tensor_memory(geometry):
+    """The tcgen05 prompt kernel: packed prompts that start at position 0, of lengths on
+    both sides of its 128-row tiles, with a far key that long sequences must find and a
+    window whose edge falls inside a tile."""
+    from kidi_b200.kernels import attention
+    heads, kv_heads, head_dim, window = geometry
+    scale = 1.0 / math.sqrt(head_dim)
+    lengths = [300, 1, 128, 129, 700, 64]
+    starts = [0] * len(lengths)
+    cache, slots, plan, tables = make_cache_and_tables(starts, lengths, kv_heads, head_dim, window, torch.bfloat16,
+                                                       max_tokens=8192)
+    generator = torch.Generator().manual_seed(head_dim + heads)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = torch.zeros(plan.n_rows, width)
+    history = {}
+    for index, length in enumerate(lengths):
+        row0 = int(plan.seq_row0[index])
+        keys = torch.randn(length, kv_heads, head_dim, generator=generator)
+        values = torch.randn(length, kv_heads, head_dim, generator=generator)
+        q = torch.randn(length, heads, head_dim, generator=generator)
+        if length > 150:
+            keys[7] *= 0.0
+            keys[7, :, 0] = 30.0
+            q[:, :, 0] = 4.0
+        history[index] = (keys.to(torch.bfloat16).float(), values.to(torch.bfloat16).float())
+        qkv[row0:row0 + length, :heads * head_dim] = q.reshape(length, -1)
+        qkv[row0:row0 + length, heads * head_dim:(heads + kv_heads) * head_dim] = keys.reshape(length, -1)
+        qkv[row0:row0 + length, (heads + kv_heads) * head_dim:] = values.reshape(length, -1)
+    qkv = qkv.to(torch.bfloat16)
+    device_qkv = qkv.to(DEVICE)
+    out = torch.full((plan.n_rows, heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEVICE)
+    assert attention.tensor_memory_fits(device_qkv, out, head_dim, heads, kv_heads)
+    attention.prefill_tensor_memory(device_qkv, out, tables.seq_len, tables.seq_row0, plan.n_seqs, plan.max_new,
+                                    heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
+    torch.cuda.synchronize()
+    assert attention.timeout_flags() == 0
+    for index, length in enumerate(lengths):
+        row0 = int(plan.seq_row0[index])
+        keys, values = history[index]
+        q = qkv[row0:row0 + length, :heads * head_dim].float().reshape(length, heads, head_dim)
+        expected = reference_attention(q, keys, values, plan.row_pos[row0:row0 + length], window, scale)
+        close(out[row0:row0 + length], expected, 1e-2, f"sequence {index} of {length} tokens")
+    # The dispatcher takes this kernel for such a step and agrees with itself.
+    again = torch.empty_like(out)
+    launch_attention("tensor_core", plan, tables, device_qkv, again, heads=heads, kv_heads=kv_heads,
+                     head_dim=head_dim, scale=scale, window=window, kv_view=cache.views(0)[0], keys_in_step=True)
+    assert torch.equal(again, out)
+
+
 def test_window_edge():
     """The key just outside the window must not be seen, the one just inside must."""
     from kidi_b200.kernels import ops

@@ -26,6 +26,7 @@ LENGTHS = {
     "tiny_a": [1, 5, 33, 64, 65, 97, 128],
     "tiny_b": [1, 7, 17, 31, 66, 129, 200, 256],
     "tiny_c": [2, 40, 71, 141, 250, 320],
+    "tiny_d": [3, 127, 128, 129, 300, 420],
 }
 
 

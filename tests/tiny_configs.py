@@ -35,4 +35,16 @@ TINY_C = {
     "sliding_window": 70,
 }
 
-ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
+# Five layers, 3 heads over one key/value head (group 3), head width 64: the width at which
+# the bfloat16 engine runs prompts through its tensor-memory attention kernel, whose tiles
+# are 128 rows; two layers have a window of 150 tokens, whose edge falls inside a tile.
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu",
+    "num_hidden_layers": 5, "hidden_size": 80, "num_attention_heads": 3, "num_key_value_heads": 1,
+    "head_dim": 64, "intermediate_size": 152, "vocab_size": 211, "rope_theta": 200000.0,
+    "rms_norm_eps": 2e-6, "tie_word_embeddings": True, "max_position_embeddings": 448,
+    "layer_types": ["sliding_attention", "full_attention", "full_attention", "sliding_attention", "full_attention"],
+    "sliding_window": 150,
+}
+
+ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
