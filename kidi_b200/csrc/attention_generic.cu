@@ -115,27 +115,33 @@ __global__ void __launch_bounds__(128) rope_store_kernel(RopeStoreArgs a) {
     }
 }
 
-// The same for bfloat16 rows in 16-byte vectors: lane l owns elements 8l..8l+7 of the head,
-// and its rotation partners are the eight elements of lane l +- half/8, fetched with
-// shuffles. Needs head_dim and rotary_dim/2 to be multiples of 8 and 16-byte aligned rows.
+// The same for bfloat16 rows in 16-byte vectors. A (row, head) is handled by a group of
+// L lanes (L the power of two that covers head_dim / 8: 16 lanes for a head of 128), so a
+// warp takes 32 / L of them; lane l of a group owns elements 8l..8l+7 of the head, and its
+// rotation partners are the eight elements of lane l +- half/8, fetched with shuffles.
+// Needs head_dim and rotary_dim/2 to be multiples of 8 and 16-byte aligned rows.
 template <typename TW>
-__global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a) {
+__global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a, int group_lanes) {
     pdl_prologue();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_heads = a.heads + 2 * a.kv_heads;
-    const long long item = (long long)blockIdx.x * 4 + warp;
-    if (item >= (long long)a.rows * total_heads) return;
-    const int row = (int)(item / total_heads);
-    const int head = (int)(item - (long long)row * total_heads);
+    const int per_warp = 32 / group_lanes;
+    const int group = lane / group_lanes, l = lane - group * group_lanes;
+    const long long item = ((long long)blockIdx.x * 4 + warp) * per_warp + group;
+    // Every lane stays to the end (the shuffles are warp-wide); `alive` says whether the
+    // group has a (row, head) to work on.
+    bool alive = item < (long long)a.rows * total_heads;
+    const int row = alive ? (int)(item / total_heads) : 0;
+    const int head = alive ? (int)(item - (long long)row * total_heads) : 0;
     const int seq = a.row_seq[row];
-    if (seq < 0) return;
+    alive = alive && seq >= 0;
     const int position = a.row_pos[row];
-    const int d = a.head_dim, c0 = 8 * lane;
-    const bool mine = c0 < d;
+    const int d = a.head_dim, c0 = 8 * l;
+    const bool mine = alive && c0 < d;
     bf16* vector = (bf16*)a.qkv + row * a.ld + (long long)head * d;
 
     bf16* cached = nullptr;
-    if (head >= a.heads && a.k_cache) {
+    if (alive && head >= a.heads && a.k_cache) {
         bool keep = true;
         if (a.cache.ring_pages) {
             const int ring_tokens = a.cache.ring_pages << a.cache.page_shift;
@@ -150,10 +156,8 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a) {
     }
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (mine) raw = *reinterpret_cast<const uint4*>(vector + c0);
-    if (head >= a.heads + a.kv_heads || !a.transform) {  // a value head, or copy only
-        if (cached && mine) *reinterpret_cast<uint4*>(cached + c0) = raw;
-        return;
-    }
+    const bool plain = head >= a.heads + a.kv_heads || !a.transform;  // a value head, or copy only
+    if (plain && cached && mine) *reinterpret_cast<uint4*>(cached + c0) = raw;
     const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
     float v[8];
     float square = 0.f;
@@ -166,20 +170,23 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a) {
         square = fmaf(two.y, two.y, square);
     }
     const TW* weight = (const TW*)(head < a.heads ? a.q_norm : a.k_norm);
-    if (weight) {
-        const float inv = 1.0f / sqrtf(warp_sum(square) / (float)d + a.eps);
-        if (mine)
+    if (a.q_norm || a.k_norm) {      // the same for the whole launch: the shuffles stay warp-wide
+        for (int offset = group_lanes >> 1; offset > 0; offset >>= 1)
+            square += __shfl_xor_sync(0xffffffffu, square, offset);
+        if (weight && mine && !plain) {
+            const float inv = 1.0f / sqrtf(square / (float)d + a.eps);
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * to_float(weight[c0 + i]);
+        }
     }
     if (a.cos_table) {
         const int half = a.rotary_dim / 2;
         const bool low = c0 < half;
-        const int partner = low ? lane + half / 8 : lane - half / 8;
+        const int partner = group * group_lanes + ((low ? l + half / 8 : l - half / 8) & (group_lanes - 1));
         float other[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) other[i] = __shfl_sync(0xffffffffu, v[i], partner & 31);
-        if (mine && c0 < a.rotary_dim) {
+        for (int i = 0; i < 8; ++i) other[i] = __shfl_sync(0xffffffffu, v[i], partner);
+        if (mine && !plain && c0 < a.rotary_dim) {
             const int j = low ? c0 : c0 - half;
             const float4* cosine = reinterpret_cast<const float4*>(a.cos_table + (long long)position * half + j);
             const float4* sine = reinterpret_cast<const float4*>(a.sin_table + (long long)position * half + j);
@@ -190,7 +197,7 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a) {
             for (int i = 0; i < 8; ++i) v[i] = v[i] * c8[i] + (low ? -other[i] : other[i]) * s8[i];
         }
     }
-    if (mine) {
+    if (mine && !plain) {
         uint4 packed;
         __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
@@ -210,8 +217,16 @@ KIDI_API int kidi_rope_store(const RopeStoreArgs* args, int dtype, int norm_dtyp
                          !((uintptr_t)a.k_cache & 15) && !((uintptr_t)a.v_cache & 15) &&
                          (!a.cos_table || (!(a.rotary_dim & 15) && !((uintptr_t)a.cos_table & 15) &&
                                            !((uintptr_t)a.sin_table & 15)));
-    if (vectors && norm_dtype == KIDI_F32) return kidi_launch(rope_store_bf16_kernel<float>, blocks, 128, 0, stream, a);
-    if (vectors && norm_dtype == KIDI_BF16) return kidi_launch(rope_store_bf16_kernel<bf16>, blocks, 128, 0, stream, a);
+    if (vectors) {
+        int group_lanes = 1;                    // lanes that cover a head in 16-byte vectors
+        while (group_lanes * 8 < a.head_dim) group_lanes <<= 1;
+        const long long per_block = 4 * (32 / group_lanes);
+        const unsigned vector_blocks = (unsigned)((items + per_block - 1) / per_block);
+        if (norm_dtype == KIDI_F32)
+            return kidi_launch(rope_store_bf16_kernel<float>, vector_blocks, 128, 0, stream, a, group_lanes);
+        if (norm_dtype == KIDI_BF16)
+            return kidi_launch(rope_store_bf16_kernel<bf16>, vector_blocks, 128, 0, stream, a, group_lanes);
+    }
     if (dtype == KIDI_F32 && norm_dtype == KIDI_F32) return kidi_launch(rope_store_kernel<float, float>, blocks, 128, 0, stream, a);
     if (dtype == KIDI_F32 && norm_dtype == KIDI_BF16) return kidi_launch(rope_store_kernel<float, bf16>, blocks, 128, 0, stream, a);
     if (dtype == KIDI_BF16 && norm_dtype == KIDI_F32) return kidi_launch(rope_store_kernel<bf16, float>, blocks, 128, 0, stream, a);

@@ -97,7 +97,9 @@ def _digest(sources: Sequence[str], flags: Sequence[str]) -> str:
         digest.update(name.encode())
         with open(os.path.join(SOURCE_DIR, name), "rb") as handle:
             digest.update(handle.read())
-    digest.update("\0".join(flags).encode())
+    # The include path is where this checkout lies: a library built in one place is the same
+    # library in a copy of the tree elsewhere.
+    digest.update("\0".join(flag for flag in flags if flag != SOURCE_DIR).encode())
     return digest.hexdigest()[:16]
 
 
@@ -116,6 +118,20 @@ def _compile(nvcc: str, source: str, obj: str, flags: Sequence[str]) -> None:
     result = subprocess.run(command, capture_output=True, text=True)
     if result.returncode != 0:
         raise runtime_error(f"nvcc failed on {source}:\n{' '.join(command)}\n{result.stdout}\n{result.stderr}")
+
+
+def _remove_older_builds(folder: str, name: str, keep: str) -> None:
+    """Drops the shared objects of earlier versions of a library's sources (a process that
+    has one loaded keeps its mapping)."""
+    prefix = f"libkidi_{name}_"
+    for entry in os.listdir(folder):
+        path = os.path.join(folder, entry)
+        stem = entry[len(prefix):-3] if entry.startswith(prefix) and entry.endswith(".so") else ""
+        if path != keep and len(stem) == 16 and all(c in "0123456789abcdef" for c in stem):
+            try:
+                os.remove(path)
+            except OSError:
+                pass
 
 
 def build_library(name: str, sources: Sequence[str], defines: Optional[Mapping[str, object]] = None,
@@ -156,6 +172,7 @@ def build_library(name: str, sources: Sequence[str], defines: Optional[Mapping[s
                 if result.returncode != 0:
                     raise runtime_error(f"linking '{name}' failed:\n{result.stdout}\n{result.stderr}")
                 os.replace(partial, target)
+                _remove_older_builds(folder, name, keep=target)
             finally:
                 stop.set()
                 shutil.rmtree(work, ignore_errors=True)
