@@ -17,6 +17,8 @@
 // V, which accumulates in 32-bit. Formulas: src/kidi/layers/qwen3.cpp:53-54,
 // src/kidi/runtime/vulkan/attention.comp:32-101; causal rule
 // src/kidi/model/gemma4.cpp:736-740.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "attention_no_alloc.h"
 
@@ -35,6 +37,7 @@ constexpr int TILE = 64;                // keys per tile = cache page size
 constexpr int CHUNKS = D / 8;           // 16-byte chunks per row
 constexpr int THREADS = 128;
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr int NARROW_STAT_FLOATS = 4 * 8 * 2 + 2 * 8 * 32 + 8;   // the narrow decode kernel's merge statistics
 
 __device__ __forceinline__ unsigned smem_address(const void* pointer) {
     return (unsigned)__cvta_generic_to_shared(pointer);
@@ -449,7 +452,7 @@ __device__ __forceinline__ void bulk_copy_row(void* shared, const void* global, 
 // One 64-row tile of keys and one of values, a bulk copy per row (rows are contiguous in
 // the cache and padded in shared memory): threads 0..63 bring key rows, 64..127 value
 // rows, thread 0 tells the barrier how many bytes to expect. Rows beyond `rows_valid`
-// are left as they are (zeros, or an earlier tile's finite values; their scores are masked).
+// are left as they are (their scores are masked; the caller keeps their values finite).
 __device__ __forceinline__ void issue_tile(bf16* k_tile, bf16* v_tile, const bf16* k_cache, const bf16* v_cache,
                                            const CacheGeometry& geometry, int slot, int kv_head, int tile,
                                            int rows_valid, unsigned long long* bar) {
@@ -486,6 +489,10 @@ __device__ __forceinline__ unsigned transpose_8x8(unsigned packed) {
     return out;
 }
 
+// CLUSTER: the blocks that share a (row, key/value head), one per split, form a thread-block
+// cluster and merge their partial results through distributed shared memory (no trip
+// through global memory, no second kernel); at most 8 splits.
+template <bool CLUSTER>
 __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a) {
     extern __shared__ __align__(16) unsigned char raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(raw);            // [8][PITCH] (16 rows reserved)
@@ -526,9 +533,17 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&tile_bar[1])));
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
-        // The tiles start as zeros: rows that no copy ever writes must be finite.
-        for (int chunk = threadIdx.x; chunk < 4 * TILE * PITCH / 8; chunk += THREADS)
-            reinterpret_cast<uint4*>(k_tiles)[chunk] = make_uint4(0u, 0u, 0u, 0u);
+        // Value rows that no copy writes must be finite (their weights are exact zeros; a
+        // masked score is replaced whatever its key row holds). Only the sequence's last tile
+        // can be short, and only while a buffer has not yet held a whole tile can its rows be
+        // unwritten: the rows past the end of the block's first two tiles are zeroed.
+        for (int index = 0; index < 2 && index < tiles; ++index) {
+            const int valid = min(TILE, position - (tile_first + index) * TILE + 1);
+            for (int chunk = threadIdx.x; chunk < (TILE - valid) * CHUNKS; chunk += THREADS) {
+                const int r = valid + chunk / CHUNKS, c = chunk % CHUNKS;
+                *reinterpret_cast<uint4*>(v_tiles + (index * TILE + r) * PITCH + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
         for (int chunk = threadIdx.x; chunk < 8 * CHUNKS; chunk += THREADS) {
             const int r = chunk / CHUNKS, c = chunk - r * CHUNKS;
             const bool valid = r < group;
@@ -629,6 +644,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
     // Merge the four warps in warp order through shared memory (the tiles are free now).
     float* merge_out = reinterpret_cast<float*>(k_tiles);                // [4][8][D]
     float* merge_stat = merge_out + 4 * 8 * D;                           // [4][8][2]
+    float* block_out = merge_stat + NARROW_STAT_FLOATS;                  // [8][D]: this block's partial result
+    float* block_stat = block_out + 8 * D;                               // [8][2]
     __syncthreads();
 #pragma unroll
     for (int n = 0; n < D / 16; ++n) {
@@ -662,6 +679,12 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
         if (a.splits == 1) {
             a.out[(long long)row * a.ldo + (long long)head * D + c] =
                 from_float<bf16>(total > 0.f ? value / total : 0.f);
+        } else if (CLUSTER) {
+            block_out[r * D + c] = value;
+            if (c == 0) {
+                block_stat[r * 2] = top;
+                block_stat[r * 2 + 1] = total;
+            }
         } else {
             const long long where = ((long long)row * a.heads + head) * a.splits + split;
             a.partial_out[where * D + c] = value;
@@ -670,6 +693,42 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
                 a.partial_stat[where * 2 + 1] = total;
             }
         }
+    }
+    if (CLUSTER && a.splits > 1) {
+        // Every block of the cluster holds its partial result in shared memory; each merges a
+        // share of the output elements, reading the others' partials in split order (so the
+        // result does not depend on timing).
+        cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+        cluster.sync();
+        const int splits = a.splits;                   // == the cluster's size, <= 8
+        const int share = (group * D + splits - 1) / splits;
+        const int begin = split * share, end = min(group * D, begin + share);
+        for (int item = begin + threadIdx.x; item < end; item += THREADS) {
+            const int r = item / D, c = item - r * D;
+            float maxima[8], sums[8], top = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                if (sp < splits) {
+                    const float* stat = cluster.map_shared_rank(block_stat, sp);
+                    maxima[sp] = stat[r * 2];
+                    sums[sp] = stat[r * 2 + 1];
+                    top = fmaxf(top, maxima[sp]);
+                }
+            }
+            float total = 0.f, value = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                if (sp < splits) {
+                    const float factor = maxima[sp] == -INFINITY ? 0.f : exp2f(maxima[sp] - top);
+                    total += sums[sp] * factor;
+                    value += cluster.map_shared_rank(block_out, sp)[r * D + c] * factor;
+                }
+            }
+            a.out[(long long)row * a.ldo + (long long)(head0 + r) * D + c] =
+                from_float<bf16>(total > 0.f ? value / total : 0.f);
+        }
+        cluster.sync();                                // nobody leaves while its partials are being read
+        return;
     }
     if (a.splits > 1 && a.counters) {
         // The block that finishes last for this (row, key/value head) merges the splits: in
@@ -750,7 +809,10 @@ __global__ void attention_combine_kernel(Args a) {
 constexpr size_t PREFILL_SHARED = (size_t)(TILE + 4 * TILE) * PITCH * sizeof(bf16);
 constexpr size_t DECODE_TILES = (size_t)(16 + 4 * TILE) * PITCH * sizeof(bf16);
 constexpr size_t DECODE_MERGE = (size_t)16 * PITCH * sizeof(bf16) + (size_t)(4 * 16 * D + 4 * 16 * 2 + 2 * 8 * 32 + 8) * sizeof(float);
-constexpr size_t DECODE_SHARED = DECODE_TILES > DECODE_MERGE ? DECODE_TILES : DECODE_MERGE;
+constexpr size_t NARROW_MERGE = (size_t)16 * PITCH * sizeof(bf16) +
+                                (size_t)(4 * 8 * D + NARROW_STAT_FLOATS + 8 * D + 16) * sizeof(float);
+constexpr size_t DECODE_LARGER = DECODE_TILES > DECODE_MERGE ? DECODE_TILES : DECODE_MERGE;
+constexpr size_t DECODE_SHARED = DECODE_LARGER > NARROW_MERGE ? DECODE_LARGER : NARROW_MERGE;
 
 bool aligned(const Args& a) {
     return !((uintptr_t)a.q & 15) && !((uintptr_t)a.k_step & 15) && !((uintptr_t)a.v_step & 15) &&
@@ -793,21 +855,30 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
     if (a.rows <= 0) return 0;
     const int group = a.kv_heads > 0 ? a.heads / a.kv_heads : 0;
     if (a.cache.head_dim != D || a.heads % a.kv_heads || group > 16 || a.kv_heads > 65535 || a.rows > 65535 ||
-        !aligned(a) || a.cache.page_shift != 6 || a.splits < 1 || (a.splits > 1 && (!a.partial_out || !a.partial_stat)) ||
-        (a.counters && a.splits > 32))
+        !aligned(a) || a.cache.page_shift != 6 || a.splits < 1 || (a.counters && a.splits > 32))
         return KIDI_REFUSED_SIZE;
+    // Without a workspace the splits merge inside a thread-block cluster.
+    const bool clustered = a.splits > 1 && !a.partial_out && !a.partial_stat;
+    if (clustered && (group > 8 || a.splits > 8)) return KIDI_REFUSED_SIZE;
+    if (a.splits > 1 && !clustered && (!a.partial_out || !a.partial_stat)) return KIDI_REFUSED_SIZE;
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   (int)DECODE_SHARED);
         if (status == cudaSuccess)
-            status = cudaFuncSetAttribute(attention_decode_narrow_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)DECODE_SHARED);
+            status = cudaFuncSetAttribute(attention_decode_narrow_kernel<false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SHARED);
+        if (status == cudaSuccess)
+            status = cudaFuncSetAttribute(attention_decode_narrow_kernel<true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SHARED);
         if (status != cudaSuccess) return (int)status;
         configured = true;
     }
     dim3 grid(a.splits, a.kv_heads, a.rows);
-    int status = group <= 8 ? kidi_launch(attention_decode_narrow_kernel, grid, THREADS, DECODE_SHARED, stream, a)
+    if (clustered)
+        return kidi_launch_clusters(attention_decode_narrow_kernel<true>, grid, THREADS, DECODE_SHARED, stream,
+                                    (unsigned)a.splits, a);
+    int status = group <= 8 ? kidi_launch(attention_decode_narrow_kernel<false>, grid, THREADS, DECODE_SHARED, stream, a)
                             : kidi_launch(attention_decode_kernel, grid, THREADS, DECODE_SHARED, stream, a);
     if (status || a.splits == 1 || (group <= 8 && a.counters)) return status;
     dim3 combine(a.heads, a.rows);

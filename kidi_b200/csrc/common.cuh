@@ -122,3 +122,26 @@ static inline int kidi_launch(void (*kernel)(Expected...), dim3 grid, dim3 block
     cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<Expected>(arguments)...);
     return status != cudaSuccess ? (int)status : (int)cudaGetLastError();
 }
+
+// The same with the blocks along x grouped into thread-block clusters of `cluster_x`
+// (the grid's x extent must be a multiple of it; at most 8).
+template <typename... Expected, typename... Actual>
+static inline int kidi_launch_clusters(void (*kernel)(Expected...), dim3 grid, dim3 block, size_t shared,
+                                       cudaStream_t stream, unsigned cluster_x, Actual&&... arguments) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = cluster_x;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = kidi_pdl_flag ? 2 : 1;
+    cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<Expected>(arguments)...);
+    return status != cudaSuccess ? (int)status : (int)cudaGetLastError();
+}

@@ -21,6 +21,9 @@ from .ops import CacheGeometry, _check, c_float, c_int, c_longlong, c_void_p, ca
 
 FORCE_GENERIC = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1"
 FUSED_MERGE = os.environ.get("KIDI_B200_FUSED_MERGE", "1") == "1"
+# Up to this many splits merge inside a thread-block cluster (no workspace, no second kernel);
+# 0 switches that off.
+CLUSTER_SPLITS = int(os.environ.get("KIDI_B200_CLUSTER_SPLITS", "8"))
 TENSOR_MEMORY_PREFILL = os.environ.get("KIDI_B200_TCGEN05_ATTENTION", "1") == "1"
 TENSOR_MEMORY_HEAD_DIMS = (64, 128)
 
@@ -162,19 +165,25 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
     if decode:
         longest = min(plan.max_total, int(window)) + 64 if window else plan.max_total
         splits = getattr(ctx, "decode_splits", None) or decode_splits(qkv.shape[0], kv_heads, longest, qkv.device)
-        if splits > 1:
+        # One wave of blocks and few splits: the blocks of a (row, key/value head) form a
+        # thread-block cluster and merge through distributed shared memory (measured 13.5
+        # against 17.1 us a layer at batch 8). Clusters that must wait for several free slots of
+        # one GPC at once lose that again when the grid takes more than a wave (70.6 against
+        # 67.0 us at batch 64).
+        one_wave = qkv.shape[0] * kv_heads * splits <= BLOCKS_PER_SM * sm_count(qkv.device)
+        clustered = 1 < splits <= CLUSTER_SPLITS and heads // kv_heads <= 8 and one_wave
+        if splits > 1 and not clustered:
             workspace = ctx.workspace("attention_partial", qkv.shape[0] * heads * splits * (head_dim + 2))
             args.partial_out = workspace.data_ptr()
             args.partial_stat = workspace.data_ptr() + qkv.shape[0] * heads * splits * head_dim * 4
             # One wave of blocks: the last block of each (row, key/value head) merges its splits
             # at the kernel's tail. More waves: a second kernel merges (the fence and the counter
             # would hold up every block's slot; measured 6.55 against 6.39 ms per step at batch 64).
-            one_wave = qkv.shape[0] * kv_heads * splits <= BLOCKS_PER_SM * sm_count(qkv.device)
             if heads // kv_heads <= 8 and splits <= 32 and FUSED_MERGE and one_wave:
                 # Zeroed when it is made; the kernel leaves every counter at zero.
                 args.counters = ctx.workspace("attention_counters", qkv.shape[0] * kv_heads, zero=True).data_ptr()
         args.splits = splits
         _check(lib.kidi_attention_decode(ctypes.byref(args), stream), "attention_decode",
-               2 if splits > 1 and not args.counters else 1)
+               2 if splits > 1 and not clustered and not args.counters else 1)
     else:
         _check(lib.kidi_attention_prefill(ctypes.byref(args), plan.max_new, stream), "attention_prefill")

@@ -410,6 +410,20 @@ def test_attention_decode(kind, dtype, geometry, splits):
         q = qkv[index:index + 1, :heads * head_dim].float().reshape(1, heads, head_dim)
         expected = reference_attention(q, keys, values, [start], window, scale)
         close(out[index:index + 1], expected, tolerance, f"{kind}: sequence of {start + 1} tokens, {splits} splits")
+    if kind == "tensor_core" and splits == 3:
+        # Three splits merge inside a thread-block cluster; the same splits merged through a
+        # workspace in global memory must agree.
+        from kidi_b200.kernels import attention
+        assert attention.CLUSTER_SPLITS >= 3
+        through_workspace = torch.empty_like(out)
+        saved, attention.CLUSTER_SPLITS = attention.CLUSTER_SPLITS, 0
+        try:
+            launch_attention(kind, plan, tables, qkv.to(DEVICE), through_workspace, splits=splits, heads=heads,
+                             kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window, kv_view=view,
+                             keys_in_step=False)
+        finally:
+            attention.CLUSTER_SPLITS = saved
+        close(out, through_workspace, 8e-3, "cluster merge against workspace merge")  # one bfloat16 step
 
 
 @pytest.mark.parametrize("geometry", [(8, 2, 128, None), (4, 4, 64, None), (6, 1, 128, 200), (2, 2, 64, 130),
