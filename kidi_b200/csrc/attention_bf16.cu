@@ -95,6 +95,18 @@ struct Args {
     float* partial_stat;  // [rows, heads, splits, 2]  (maximum in log2 units, denominator)
     int splits;
     int* counters;        // [rows, kv_heads], zero between calls: the last block of a (row, kv head) merges its splits
+    // decode with eight query heads a key/value head at most: the step's rows come as the
+    // projection left them (q at `q`, the new key and value rows at k_step and v_step), and
+    // the kernel normalises and rotates them itself and writes the new key and value to
+    // the cache (src/kidi/layers/qwen3.cpp:46-57: norm, then rotation, then attention).
+    int fuse;             // bit 0: normalise and rotate q and the new k; bit 1: write the new k and v to the cache
+    int norm_is_float;    // the norm weights are float32 (else bfloat16)
+    const void* q_norm;   // [D] or null
+    const void* k_norm;
+    const float* cos_table;   // [positions, rotary_dim / 2] or null
+    const float* sin_table;
+    int rotary_dim;
+    float eps;
 };
 
 // Loads one 64 x D tile of keys (or values) for absolute key positions [tile*64, tile*64+64)
@@ -489,6 +501,73 @@ __device__ __forceinline__ unsigned transpose_8x8(unsigned packed) {
     return out;
 }
 
+// Eight elements c0..c0+7 of a head, normalised and rotated as the separate kernel does it
+// (rope_store_bf16_kernel: the same operations in the same order, in 32-bit): `own` holds
+// them as the projection left them, `partner` the eight elements half a rotation away,
+// `square_sum` the sum of squares over the whole head.
+__device__ __forceinline__ uint4 normalise_rotate(uint4 own, uint4 partner, float square_sum, const Args& a,
+                                                  const void* weight, int c0, int position) {
+    const __nv_bfloat162* mine = reinterpret_cast<const __nv_bfloat162*>(&own);
+    const __nv_bfloat162* theirs = reinterpret_cast<const __nv_bfloat162*>(&partner);
+    float v[8], other[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(mine[i]), y = __bfloat1622float2(theirs[i]);
+        v[2 * i] = x.x; v[2 * i + 1] = x.y;
+        other[2 * i] = y.x; other[2 * i + 1] = y.y;
+    }
+    const int half = a.rotary_dim / 2;
+    const bool low = c0 < half;
+    const int partner_c0 = low ? c0 + half : c0 - half;
+    if (weight) {
+        const float inv = 1.0f / sqrtf(square_sum / (float)D + a.eps);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float w = a.norm_is_float ? ((const float*)weight)[c0 + i] : to_float(((const bf16*)weight)[c0 + i]);
+            v[i] = v[i] * inv * w;
+        }
+        if (a.cos_table && c0 < a.rotary_dim) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float w = a.norm_is_float ? ((const float*)weight)[partner_c0 + i]
+                                                : to_float(((const bf16*)weight)[partner_c0 + i]);
+                other[i] = other[i] * inv * w;
+            }
+        }
+    }
+    if (a.cos_table && c0 < a.rotary_dim) {
+        const int j = low ? c0 : c0 - half;
+        const float4* cosine = reinterpret_cast<const float4*>(a.cos_table + (long long)position * half + j);
+        const float4* sine = reinterpret_cast<const float4*>(a.sin_table + (long long)position * half + j);
+        const float4 ca = cosine[0], cb = cosine[1], sa = sine[0], sb = sine[1];
+        const float c8[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+        const float s8[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = v[i] * c8[i] + (low ? -other[i] : other[i]) * s8[i];
+    }
+    uint4 packed;
+    __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) out[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    return packed;
+}
+
+// The sum of squares of a head of which lane l holds elements 8l..8l+7 (lanes past the
+// head hold zeros), added in the order of the separate kernel.
+__device__ __forceinline__ float head_square_sum(uint4 own) {
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&own);
+    float square = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 two = __bfloat1622float2(pairs[i]);
+        square = fmaf(two.x, two.x, square);
+        square = fmaf(two.y, two.y, square);
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) square += __shfl_xor_sync(0xffffffffu, square, offset);
+    return square;
+}
+
 // CLUSTER: the blocks that share a (row, key/value head), one per split, form a thread-block
 // cluster and merge their partial results through distributed shared memory (no trip
 // through global memory, no second kernel); at most 8 splits.
@@ -553,20 +632,49 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
         copy_async_commit();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
-        issue_tile(k_tiles, v_tiles, a.k_cache, a.v_cache, a.cache, slot, kv_head, tile_first,
-                   min(TILE, position - tile_first * TILE + 1), &tile_bar[0]);
+        // With the rotation fused the step's own key and value are not in the cache yet: the
+        // block whose last tile holds position `position` computes them, puts them into its
+        // tile and (bit 1) into the cache; the copies leave that row out.
+        const int new_tile = position / TILE;
+        const bool has_new = a.fuse != 0 && tile_first + tiles - 1 == new_tile;
+        uint4 new_raw = make_uint4(0u, 0u, 0u, 0u);          // warp 0: the new key row's chunk, warp 1: the value's
+        if (has_new && warp < 2 && lane < CHUNKS)
+            new_raw = *reinterpret_cast<const uint4*>((warp == 0 ? a.k_step : a.v_step) + (long long)row * a.ldkv +
+                                                      (long long)kv_head * D + lane * 8);
+        auto rows_to_copy = [&](int tile) {
+            return min(TILE, position - tile * TILE + 1) - (a.fuse != 0 && tile == new_tile ? 1 : 0);
+        };
+        issue_tile(k_tiles, v_tiles, a.k_cache, a.v_cache, a.cache, slot, kv_head, tile_first, rows_to_copy(tile_first),
+                   &tile_bar[0]);
         const float scale_log2 = a.scale * LOG2E;
         unsigned q_frag[D / 16][2];                         // Q^T as B operand: (dims, head g)
         for (int index = 0; index < tiles; ++index) {
             const int tile = tile_first + index, buffer = index & 1;
             if (index + 1 < tiles)                          // the other buffer was read in the step before
                 issue_tile(k_tiles + (buffer ^ 1) * TILE * PITCH, v_tiles + (buffer ^ 1) * TILE * PITCH, a.k_cache,
-                           a.v_cache, a.cache, slot, kv_head, tile + 1, min(TILE, position - (tile + 1) * TILE + 1),
-                           &tile_bar[buffer ^ 1]);
+                           a.v_cache, a.cache, slot, kv_head, tile + 1, rows_to_copy(tile + 1), &tile_bar[buffer ^ 1]);
             wait_tile(&tile_bar[buffer], (index >> 1) & 1);
             if (index == 0) {
                 copy_async_wait<0>();
                 __syncthreads();
+                if (a.fuse & 1) {                           // q as the projection left it: norm, then rotation
+                    const int half_lanes = a.rotary_dim / 16;
+                    const int partner_lane = (lane * 8 < a.rotary_dim / 2 ? lane + half_lanes : lane - half_lanes) & 31;
+                    for (int r = warp; r < group; r += 4) {
+                        uint4 own = make_uint4(0u, 0u, 0u, 0u);
+                        if (lane < CHUNKS) own = *reinterpret_cast<const uint4*>(q_tile + r * PITCH + lane * 8);
+                        const float square = head_square_sum(own);
+                        uint4 partner;
+                        partner.x = __shfl_sync(0xffffffffu, own.x, partner_lane);
+                        partner.y = __shfl_sync(0xffffffffu, own.y, partner_lane);
+                        partner.z = __shfl_sync(0xffffffffu, own.z, partner_lane);
+                        partner.w = __shfl_sync(0xffffffffu, own.w, partner_lane);
+                        if (lane < CHUNKS)
+                            *reinterpret_cast<uint4*>(q_tile + r * PITCH + lane * 8) =
+                                normalise_rotate(own, partner, square, a, a.q_norm, lane * 8, position);
+                    }
+                    __syncthreads();
+                }
 #pragma unroll
                 for (int kk = 0; kk < D / 32; ++kk) {       // two 16-dim steps per load
                     unsigned r4[4];
@@ -581,8 +689,35 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
                 }
             }
             const int first_key = warp * 16;
-            const bf16* k_tile = k_tiles + buffer * TILE * PITCH;
-            const bf16* v_tile = v_tiles + buffer * TILE * PITCH;
+            bf16* k_tile = k_tiles + buffer * TILE * PITCH;
+            bf16* v_tile = v_tiles + buffer * TILE * PITCH;
+            if (has_new && tile == new_tile) {              // the step's own key (warp 0) and value (warp 1)
+                const int r_new = position - tile * TILE;
+                if (warp < 2) {
+                    uint4 fresh = new_raw;
+                    if (warp == 0 && (a.fuse & 1)) {
+                        const int half_lanes = a.rotary_dim / 16;
+                        const int partner_lane = (lane * 8 < a.rotary_dim / 2 ? lane + half_lanes : lane - half_lanes) & 31;
+                        const float square = head_square_sum(new_raw);
+                        uint4 partner;
+                        partner.x = __shfl_sync(0xffffffffu, new_raw.x, partner_lane);
+                        partner.y = __shfl_sync(0xffffffffu, new_raw.y, partner_lane);
+                        partner.z = __shfl_sync(0xffffffffu, new_raw.z, partner_lane);
+                        partner.w = __shfl_sync(0xffffffffu, new_raw.w, partner_lane);
+                        if (lane < CHUNKS)     // lanes past the head have no weights to read
+                            fresh = normalise_rotate(new_raw, partner, square, a, a.k_norm, lane * 8, position);
+                    }
+                    if (lane < CHUNKS) {
+                        *reinterpret_cast<uint4*>((warp == 0 ? k_tile : v_tile) + r_new * PITCH + lane * 8) = fresh;
+                        if (a.fuse & 2) {
+                            bf16* cache = const_cast<bf16*>(warp == 0 ? a.k_cache : a.v_cache);
+                            *reinterpret_cast<uint4*>(cache + cache_row_offset(a.cache, slot, position, kv_head) + lane * 8) =
+                                fresh;
+                        }
+                    }
+                }
+                __syncthreads();
+            }
             if (tile * TILE + first_key <= position && tile * TILE + first_key + 15 >= low) {
                 float s[4] = {0.f, 0.f, 0.f, 0.f};          // keys g (0,1) and g+8 (2,3) x heads 2t, 2t+1
 #pragma unroll
@@ -857,6 +992,12 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
     if (a.cache.head_dim != D || a.heads % a.kv_heads || group > 16 || a.kv_heads > 65535 || a.rows > 65535 ||
         !aligned(a) || a.cache.page_shift != 6 || a.splits < 1 || (a.counters && a.splits > 32))
         return KIDI_REFUSED_SIZE;
+    if (a.fuse) {   // the rotation inside the kernel: the narrow kernel, vectors of eight elements
+        if (group > 8 || !a.k_step || !a.v_step || (a.ldkv & 7) || (a.rotary_dim & 15) || a.rotary_dim > D ||
+            a.rotary_dim < 0 || ((uintptr_t)a.cos_table & 15) || ((uintptr_t)a.sin_table & 15) ||
+            ((a.fuse & 1) && a.cos_table && !a.sin_table))
+            return KIDI_REFUSED_SIZE;
+    }
     // Without a workspace the splits merge inside a thread-block cluster.
     const bool clustered = a.splits > 1 && !a.partial_out && !a.partial_stat;
     if (clustered && (group > 8 || a.splits > 8)) return KIDI_REFUSED_SIZE;

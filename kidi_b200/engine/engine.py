@@ -51,6 +51,10 @@ class StepContext:
     def attention(self, qkv, out, **arguments) -> None:
         attention_kernels.run(self, qkv, out, **arguments)
 
+    def fuses_rotation(self, qkv, **arguments) -> bool:
+        """Whether `attention` can do norm, rotation and the cache write of this step itself."""
+        return attention_kernels.fuses_rotation(self.plan, qkv, **arguments)
+
     def workspace(self, name: str, count: int, zero: bool = False) -> torch.Tensor:
         """Scratch memory of at least `count` 32-bit elements that kernels of one step may
         use one after another (it is kept between steps and grows on demand). With `zero`

@@ -21,6 +21,9 @@ from .ops import CacheGeometry, _check, c_float, c_int, c_longlong, c_void_p, ca
 
 FORCE_GENERIC = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1"
 FUSED_MERGE = os.environ.get("KIDI_B200_FUSED_MERGE", "1") == "1"
+# One token per sequence: the decode kernel normalises and rotates q and the new key itself and
+# writes the new key and value to the cache (one kernel less per layer); 0 switches that off.
+FUSE_ROTATION = os.environ.get("KIDI_B200_FUSE_ROTATION", "1") == "1"
 # Up to this many splits merge inside a thread-block cluster (no workspace, no second kernel);
 # 0 switches that off.
 CLUSTER_SPLITS = int(os.environ.get("KIDI_B200_CLUSTER_SPLITS", "8"))
@@ -35,7 +38,9 @@ class FastAttentionArgs(ctypes.Structure):
                 ("seq_slot", c_void_p), ("seq_start", c_void_p), ("seq_len", c_void_p), ("seq_row0", c_void_p),
                 ("rows", c_int), ("seqs", c_int), ("heads", c_int), ("kv_heads", c_int), ("window", c_int),
                 ("scale", c_float), ("partial_out", c_void_p), ("partial_stat", c_void_p), ("splits", c_int),
-                ("counters", c_void_p)]
+                ("counters", c_void_p), ("fuse", c_int), ("norm_is_float", c_int), ("q_norm", c_void_p),
+                ("k_norm", c_void_p), ("cos_table", c_void_p), ("sin_table", c_void_p), ("rotary_dim", c_int),
+                ("eps", c_float)]
 
 
 _libraries: Dict[int, ctypes.CDLL] = {}
@@ -138,7 +143,29 @@ def decode_splits(rows: int, kv_heads: int, longest: int, device: torch.device) 
     return best
 
 
-def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step) -> None:
+def fuses_rotation(plan, qkv: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int, kv_view, q_norm, k_norm,
+                   cos, sin, rotary_dim: int) -> bool:
+    """Whether `run` can take the step's rows as the projection left them (`rotation=`):
+    one token per sequence over a paged bfloat16 cache, at most eight query heads per
+    key/value head, and norm weights and angle tables that 16-byte vectors can read."""
+    if not (FUSE_ROTATION and plan.is_decode and kv_view is not None and kv_view.page_size == 64
+            and fast_fits(qkv.dtype, heads, kv_heads, head_dim, True) and heads // kv_heads <= 8):
+        return False
+    if (q_norm is None) != (k_norm is None) or qkv.stride(0) % 8 or qkv.data_ptr() % 16:
+        return False
+    if q_norm is not None and (q_norm.dtype != k_norm.dtype or q_norm.dtype not in (torch.float32, torch.bfloat16)
+                               or not q_norm.is_contiguous() or not k_norm.is_contiguous()):
+        return False
+    if cos is not None and (rotary_dim % 16 or rotary_dim > head_dim or cos.dtype != torch.float32
+                            or cos.data_ptr() % 16 or sin.data_ptr() % 16 or not cos.is_contiguous()):
+        return False
+    return True
+
+
+def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step, rotation=None) -> None:
+    """`rotation` (only where `fuses_rotation` said yes): dict(q_norm, k_norm, eps, cos, sin,
+    rotary_dim, store): the kernel normalises and rotates q and the step's key and, with
+    `store`, writes the step's key and value to the cache."""
     plan, tables = ctx.plan, ctx.tables
     decode = plan.is_decode and not keys_in_step
     if not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode) or (kv_view is not None and kv_view.page_size != 64):
@@ -183,6 +210,19 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
                 # Zeroed when it is made; the kernel leaves every counter at zero.
                 args.counters = ctx.workspace("attention_counters", qkv.shape[0] * kv_heads, zero=True).data_ptr()
         args.splits = splits
+        if rotation is not None:
+            item = qkv.element_size()
+            args.k_step = qkv.data_ptr() + heads * head_dim * item
+            args.v_step = qkv.data_ptr() + (heads + kv_heads) * head_dim * item
+            args.fuse = 1 | (2 if rotation.get("store", True) else 0)
+            q_norm, k_norm, cos, sin = (rotation.get(name) for name in ("q_norm", "k_norm", "cos", "sin"))
+            if q_norm is not None:
+                args.q_norm, args.k_norm = q_norm.data_ptr(), k_norm.data_ptr()
+                args.norm_is_float = int(q_norm.dtype == torch.float32)
+            if cos is not None:
+                args.cos_table, args.sin_table = cos.data_ptr(), sin.data_ptr()
+                args.rotary_dim = int(rotation["rotary_dim"])
+            args.eps = float(rotation.get("eps", 0.0))
         _check(lib.kidi_attention_decode(ctypes.byref(args), stream), "attention_decode",
                2 if splits > 1 and not clustered and not args.counters else 1)
     else:

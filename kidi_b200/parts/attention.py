@@ -96,12 +96,18 @@ class Attention(Part):
         store_first = owns_cache and (not ring or plan.is_decode)
         if not owns_cache and ring and not plan.is_decode:
             raise unsupported("a layer that reads another layer's windowed cache takes one token per step")
-        ops.rope_store(qkv, q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, tables=ctx.tables, kv_view=view,
-                       store=store_first, **rotate, **common)
+        # One token per sequence on the tensor-core path: the attention kernel takes the rows as
+        # the projection left them and does norm, rotation and the cache write itself.
+        fused = owns_cache and store_first and ctx.fuses_rotation(qkv, kv_view=view, q_norm=self.q_norm,
+                                                                  k_norm=self.k_norm, **rotate, **common)
+        if not fused:
+            ops.rope_store(qkv, q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, tables=ctx.tables, kv_view=view,
+                           store=store_first, **rotate, **common)
         attended = torch.empty((qkv.shape[0], self.q_width), dtype=qkv.dtype, device=qkv.device)
         keys_in_step = owns_cache and not plan.is_decode
+        rotation = dict(q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, store=True, **rotate) if fused else None
         ctx.attention(qkv, attended, scale=self.scale, window=self.window, kv_view=view,
-                      keys_in_step=keys_in_step, **common)
+                      keys_in_step=keys_in_step, rotation=rotation, **common)
         if owns_cache and not store_first:
             ops.rope_store(qkv, q_norm=None, k_norm=None, eps=self.eps, tables=ctx.tables, kv_view=view, store=True,
                            transform=False, cos=None, sin=None, rotary_dim=0, **common)

@@ -477,6 +477,62 @@ def test_attention_prompts_tensor_memory(geometry):
     assert torch.equal(again, out)
 
 
+@pytest.mark.parametrize("geometry", [(8, 2, 128, None, 128), (6, 6, 48, None, 32), (16, 2, 64, 90, 64),
+                                      (4, 1, 32, None, 0)])
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("norm_dtype", [torch.bfloat16, torch.float32])
+def test_decode_with_the_rotation_inside(geometry, splits, norm_dtype):
+    """One token per sequence, given to the attention kernel as the projection left it:
+    the kernel's own norm, rotation and cache write against the separate kernel followed
+    by the same attention, on two copies of a filled cache."""
+    from kidi_b200.engine.plan import StepBatch, build_plan
+    from kidi_b200.kernels import attention, ops
+    heads, kv_heads, head_dim, window, rotary_dim = geometry
+    scale = 1.0 / math.sqrt(head_dim)
+    starts = [0, 63, 64, 300, 1000, 127]
+    news = [1] * len(starts)
+    generator = torch.Generator().manual_seed(head_dim * 11 + heads)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = torch.randn(len(starts), width, generator=generator).to(torch.bfloat16).to(DEVICE)
+    q_norm = (1 + 0.1 * torch.randn(head_dim, generator=generator)).to(norm_dtype).to(DEVICE)
+    k_norm = (1 + 0.1 * torch.randn(head_dim, generator=generator)).to(norm_dtype).to(DEVICE)
+    if rotary_dim:
+        cos, sin = plain_model.rotary_tables(2048, rotary_dim, 1e4)
+        cos, sin = cos.to(DEVICE), sin.to(DEVICE)
+    else:
+        cos = sin = None
+    results = []
+    for fused in (False, True):
+        cache, slots, plan, tables = make_cache_and_tables(starts, news, kv_heads, head_dim, window, torch.bfloat16,
+                                                           max_tokens=8192)
+        view = cache.views(0)[0]
+        filler = torch.Generator().manual_seed(5)
+        view.keys.copy_(torch.randn(view.keys.shape, generator=filler).to(torch.bfloat16))
+        view.values.copy_(torch.randn(view.values.shape, generator=filler).to(torch.bfloat16))
+        rows = qkv.clone()
+        out = torch.empty(len(starts), heads * head_dim, dtype=torch.bfloat16, device=DEVICE)
+        common = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim)
+        if fused:
+            assert attention.fuses_rotation(plan, rows, kv_view=view, q_norm=q_norm, k_norm=k_norm, cos=cos, sin=sin,
+                                            rotary_dim=rotary_dim, **common)
+            rotation = dict(q_norm=q_norm, k_norm=k_norm, eps=1e-6, cos=cos, sin=sin, rotary_dim=rotary_dim, store=True)
+        else:
+            ops.rope_store(rows, q_norm=q_norm, k_norm=k_norm, eps=1e-6, cos=cos, sin=sin, rotary_dim=rotary_dim,
+                           tables=tables, kv_view=view, store=True, **common)
+            rotation = None
+        attention.run(FakeContext(plan, tables, splits), rows, out, scale=scale, window=window, kv_view=view,
+                      keys_in_step=False, rotation=rotation, **common)
+        torch.cuda.synchronize()
+        results.append((out, view.keys.clone(), view.values.clone(), [view.group.pages[slot] for slot in slots]))
+    (plain_out, plain_keys, plain_values, plain_pages), (fused_out, fused_keys, fused_values, fused_pages) = results
+    assert plain_pages == fused_pages
+    assert torch.equal(fused_keys, plain_keys), "the keys written by the attention kernel differ from the separate kernel's"
+    assert torch.equal(fused_values, plain_values)
+    assert torch.isfinite(fused_out.float()).all()
+    close(fused_out, plain_out, 8e-3, "attention with the rotation inside")      # one bfloat16 step
+    assert attention.timeout_flags() == 0
+
+
 def test_window_edge():
     """The key just outside the window must not be seen, the one just inside must."""
     from kidi_b200.kernels import ops
