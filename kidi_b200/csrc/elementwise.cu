@@ -70,10 +70,84 @@ add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, c
         out[c] = from_float<TY>(staged[c] * inv * to_float(weight[c]));
 }
 
+// Four consecutive elements of a row as 32-bit values, whatever the stored type.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same for rows of exactly THREADS * 4 * CHUNKS elements: every thread keeps its
+// CHUNKS groups of four elements in registers, all loads of a row are in flight at once,
+// and nothing is staged in shared memory. (The sum of squares is added in this kernel's
+// own fixed order; every step of an engine with such rows takes this kernel.)
+template <typename TD, typename TW, typename TY, int THREADS, int CHUNKS>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_vector_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const TW* __restrict__ weight,
+                          TY* __restrict__ y, const int* __restrict__ row_index, float eps, int write_residual) {
+    __shared__ float scratch[32];
+    pdl_prologue();
+    constexpr int hidden = THREADS * 4 * CHUNKS;
+    const int r = blockIdx.x;
+    const long long s = row_index ? row_index[r] : r;
+    float* h = residual + s * hidden;
+    float4 v[CHUNKS];
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) v[i] = load4(h + 4 * (threadIdx.x + THREADS * i));
+    if (delta) {
+        float4 d[CHUNKS];
+#pragma unroll
+        for (int i = 0; i < CHUNKS; ++i) d[i] = load4(delta + s * hidden + 4 * (threadIdx.x + THREADS * i));
+#pragma unroll
+        for (int i = 0; i < CHUNKS; ++i) {
+            v[i].x += d[i].x; v[i].y += d[i].y; v[i].z += d[i].z; v[i].w += d[i].w;
+        }
+    }
+    float4 w[CHUNKS];
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) w[i] = load4(weight + 4 * (threadIdx.x + THREADS * i));
+    float square = 0.f;
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+        if (write_residual) store4(h + 4 * (threadIdx.x + THREADS * i), v[i]);
+        square = fmaf(v[i].x, v[i].x, square);
+        square = fmaf(v[i].y, v[i].y, square);
+        square = fmaf(v[i].z, v[i].z, square);
+        square = fmaf(v[i].w, v[i].w, square);
+    }
+    const float total = block_sum<THREADS>(square, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    TY* out = y + (long long)r * hidden;
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i)
+        store4(out + 4 * (threadIdx.x + THREADS * i),
+               make_float4(v[i].x * inv * w[i].x, v[i].y * inv * w[i].y, v[i].z * inv * w[i].z, v[i].w * inv * w[i].w));
+}
+
 template <typename TD, typename TW, typename TY>
 static int launch_add_rmsnorm(float* residual, const void* delta, const void* weight, void* y, const int* row_index,
                               int rows, int hidden, float eps, int write_residual, cudaStream_t stream) {
     constexpr int THREADS = 256;
+    const bool vectors = !((uintptr_t)residual & 15) && !((uintptr_t)delta & 15) && !((uintptr_t)weight & 15) &&
+                         !((uintptr_t)y & 15);
+#define KIDI_VECTOR_CASE(CHUNKS)                                                                              \
+    if (vectors && hidden == THREADS * 4 * CHUNKS)                                                            \
+        return kidi_launch(add_rmsnorm_vector_kernel<TD, TW, TY, THREADS, CHUNKS>, rows, THREADS, 0, stream,   \
+                           residual, (const TD*)delta, (const TW*)weight, (TY*)y, row_index, eps, write_residual);
+    KIDI_VECTOR_CASE(1)
+    KIDI_VECTOR_CASE(2)
+    KIDI_VECTOR_CASE(4)
+    KIDI_VECTOR_CASE(8)
+#undef KIDI_VECTOR_CASE
     const size_t shared = (size_t)hidden * sizeof(float);
     if (shared > 200 * 1024) return KIDI_REFUSED_SIZE;
     auto kernel = add_rmsnorm_kernel<TD, TW, TY, THREADS>;

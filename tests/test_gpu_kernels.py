@@ -38,7 +38,7 @@ def test_embedding(table_dtype):
 
 
 # -------------------------------------------------------------------- rmsnorm
-@pytest.mark.parametrize("hidden", [40, 1000, 5120])
+@pytest.mark.parametrize("hidden", [40, 1000, 1024, 4096, 5120, 8192])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(hidden, dtype):
     from kidi_b200.kernels import ops
