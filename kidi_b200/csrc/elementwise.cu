@@ -10,6 +10,22 @@
 
 KIDI_DEFINE_PDL_FLAG()
 
+// Four consecutive elements of a row as 32-bit values, whatever the stored type.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // ------------------------------------------------------------------ embedding
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
@@ -23,6 +39,13 @@ __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__
         return;
     }
     const TW* source = table + (long long)token * hidden;
+    if (!(hidden & 3) && !((uintptr_t)table & 15) && !((uintptr_t)out & 15)) {   // four elements at a time
+        for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
+            const float4 v = load4(source + c);
+            store4(destination + c, make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale));
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) destination[c] = to_float(source[c]) * scale;
 }
 
@@ -68,22 +91,6 @@ add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, c
     TY* out = y + (long long)r * hidden;
     for (int c = threadIdx.x; c < hidden; c += THREADS)
         out[c] = from_float<TY>(staged[c] * inv * to_float(weight[c]));
-}
-
-// Four consecutive elements of a row as 32-bit values, whatever the stored type.
-__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 load4(const bf16* p) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(p);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    return make_float4(a.x, a.y, b.x, b.y);
-}
-__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-__device__ __forceinline__ void store4(bf16* p, float4 v) {
-    uint2 raw;
-    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
-    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
-    *reinterpret_cast<uint2*>(p) = raw;
 }
 
 // The same for rows of exactly THREADS * 4 * CHUNKS elements: every thread keeps its
