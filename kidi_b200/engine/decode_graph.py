@@ -23,7 +23,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..errors import invalid_argument
+from ..errors import KidiError, invalid_argument
 from ..kernels import attention as attention_kernels
 from ..kernels import ops
 from .plan import StepPlan
@@ -56,6 +56,9 @@ class DecodeSession:
         self.selected = torch.zeros(capacity, dtype=torch.int32, device=device)
         self.selected_host = torch.zeros(capacity, dtype=torch.int32).pin_memory()
         self.tokens_host = torch.zeros(capacity, dtype=torch.int32).pin_memory()
+        self._tokens_host_view = self.tokens_host.numpy()
+        self._selected_host_view = self.selected_host.numpy()
+        self._reserved_ahead = False
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.live = 0
@@ -116,6 +119,7 @@ class DecodeSession:
         self.live = live
         self.slots = list(slots)
         self.positions = list(starts)
+        self._reserved_ahead = False
 
     # -------------------------------------------------------------------- step
     def _forward(self) -> None:
@@ -178,14 +182,24 @@ class DecodeSession:
         `tokens` (host integers, one per live sequence) the step's inputs are copied from
         pinned host memory first; without, the tokens selected by the previous step are
         used where they lie on the device."""
-        self.reserve(1)
+        if not self._reserved_ahead:
+            self.reserve(1)
+        self._reserved_ahead = False
         if tokens is not None:
-            self.tokens_host[:self.live] = torch.as_tensor(tokens, dtype=torch.int32)
+            self._tokens_host_view[:self.live] = tokens
             self.tables.tokens[:self.live].copy_(self.tokens_host[:self.live], non_blocking=True)
         self.launch()
         self.selected_host.copy_(self.selected, non_blocking=True)
+        # While the device runs the step, the host makes room for the next one (a sequence
+        # that turns out to have ended gives the room back with its slot). Where there is no
+        # room to take ahead of time, the next step asks again and reports it.
+        try:
+            self.reserve(1)
+            self._reserved_ahead = True
+        except KidiError:
+            pass
         torch.cuda.current_stream().synchronize()
-        return self.selected_host[:self.live].tolist()
+        return self._selected_host_view[:self.live].tolist()
 
 
 def _widest_decode(engine) -> Optional[int]:
