@@ -369,6 +369,8 @@ def test_attention_decode(kind, dtype, geometry, splits):
     heads, kv_heads, head_dim, window = geometry
     scale = 1.0 / math.sqrt(head_dim)
     starts = [0, 63, 64, 300, 1000, 127]
+    if window:  # the loud key at position 7 is the last one inside the window, then the first one outside
+        starts += [7 + window - 1, 7 + window]
     news = [1] * len(starts)
     cache, slots, plan, tables = make_cache_and_tables(starts, news, kv_heads, head_dim, window, dtype,
                                                        max_tokens=8192)
@@ -382,7 +384,7 @@ def test_attention_decode(kind, dtype, geometry, splits):
         keys = torch.randn(total, kv_heads, head_dim, generator=generator)
         values = torch.randn(total, kv_heads, head_dim, generator=generator)
         q = torch.randn(1, heads, head_dim, generator=generator)
-        if total > 150:
+        if total > 150 or index >= 6:
             keys[7] *= 0.0
             keys[7, :, 0] = 30.0
             q[:, :, 0] = 4.0
