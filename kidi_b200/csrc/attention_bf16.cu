@@ -37,7 +37,23 @@ constexpr int TILE = 64;                // keys per tile = cache page size
 constexpr int CHUNKS = D / 8;           // 16-byte chunks per row
 constexpr int THREADS = 128;
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr int NARROW_STAT_FLOATS = 4 * 8 * 2 + 2 * 8 * 32 + 8;   // the narrow decode kernel's merge statistics
+// Shared memory of a decode block: the query rows and two key and two value tiles (or, once
+// they are consumed, the warps' partial results).
+constexpr size_t DECODE_TILES = (size_t)(16 + 4 * TILE) * PITCH * sizeof(bf16);
+constexpr size_t DECODE_MERGE =
+    (size_t)16 * PITCH * sizeof(bf16) + (size_t)(4 * 16 * D + 4 * 16 * 2 + 2 * 8 * 32 + 8) * sizeof(float);
+constexpr size_t DECODE_SHARED = DECODE_TILES > DECODE_MERGE ? DECODE_TILES : DECODE_MERGE;
+// The kernel for at most eight query heads a key/value head keeps eight query rows, and
+// behind its tiles what the other blocks of a cluster send it: [splits][share] partial
+// values and [8 splits][8 heads] maxima and denominators. Three blocks of head width 128
+// fit an SM.
+constexpr int NARROW_RECV_OUT_FLOATS = 8 * D + 8;
+constexpr int NARROW_RECV_FLOATS = NARROW_RECV_OUT_FLOATS + 8 * 8 * 2;
+constexpr size_t NARROW_TILES = (size_t)(8 + 4 * TILE) * PITCH * sizeof(bf16);
+constexpr size_t NARROW_MERGE =
+    (size_t)8 * PITCH * sizeof(bf16) + (size_t)(4 * 8 * D + 4 * 8 * 2 + 2 * 8 * 32 + 8) * sizeof(float);
+constexpr size_t NARROW_TILE_BYTES = ((NARROW_TILES > NARROW_MERGE ? NARROW_TILES : NARROW_MERGE) + 15) / 16 * 16;
+constexpr size_t NARROW_SHARED = NARROW_TILE_BYTES + NARROW_RECV_FLOATS * sizeof(float);
 
 __device__ __forceinline__ unsigned smem_address(const void* pointer) {
     return (unsigned)__cvta_generic_to_shared(pointer);
@@ -348,7 +364,6 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
     // The pages of this block do not depend on the kernel before this one, except for the
     // newest token's row: they are asked into L2 before the wait for that kernel; the loads
     // into shared memory, and the query, come after it.
-    pdl_launch_dependents();
 #ifndef KIDI_ATTN_PREFETCH
 #define KIDI_ATTN_PREFETCH 0
 #endif
@@ -359,6 +374,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
         prefetch_l2(a.v_cache + offset);
     }
     pdl_wait();
+    pdl_launch_dependents();
     if (tiles > 0) {
         for (int chunk = threadIdx.x; chunk < 16 * CHUNKS; chunk += THREADS) {
             const int r = chunk / CHUNKS, c = chunk - r * CHUNKS;
@@ -574,8 +590,8 @@ __device__ __forceinline__ float head_square_sum(uint4 own) {
 template <bool CLUSTER>
 __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a) {
     extern __shared__ __align__(16) unsigned char raw[];
-    bf16* q_tile = reinterpret_cast<bf16*>(raw);            // [8][PITCH] (16 rows reserved)
-    bf16* k_tiles = q_tile + 16 * PITCH;                    // [2][64][PITCH]
+    bf16* q_tile = reinterpret_cast<bf16*>(raw);            // [8][PITCH]
+    bf16* k_tiles = q_tile + 8 * PITCH;                     // [2][64][PITCH]
     bf16* v_tiles = k_tiles + 2 * TILE * PITCH;             // [2][64][PITCH]
     pdl_prologue();
     const int split = blockIdx.x, kv_head = blockIdx.y, row = blockIdx.z;
@@ -612,10 +628,31 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&tile_bar[1])));
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
+        __syncthreads();
+        // With the rotation fused the step's own key and value are not in the cache yet: the
+        // block whose last tile holds position `position` computes them, puts them into its
+        // tile and (bit 1) into the cache; the copies leave that row out.
+        const int new_tile = position / TILE;
+        const bool has_new = a.fuse != 0 && tile_first + tiles - 1 == new_tile;
+        auto rows_to_copy = [&](int tile) {
+            return min(TILE, position - tile * TILE + 1) - (a.fuse != 0 && tile == new_tile ? 1 : 0);
+        };
+        // The first two tiles are asked for before anything else: the kernel's time is the
+        // time its keys and values take to arrive.
+        issue_tile(k_tiles, v_tiles, a.k_cache, a.v_cache, a.cache, slot, kv_head, tile_first, rows_to_copy(tile_first),
+                   &tile_bar[0]);
+        if (tiles > 1)
+            issue_tile(k_tiles + TILE * PITCH, v_tiles + TILE * PITCH, a.k_cache, a.v_cache, a.cache, slot, kv_head,
+                       tile_first + 1, rows_to_copy(tile_first + 1), &tile_bar[1]);
+        uint4 new_raw = make_uint4(0u, 0u, 0u, 0u);          // warp 0: the new key row's chunk, warp 1: the value's
+        if (has_new && warp < 2 && lane < CHUNKS)
+            new_raw = *reinterpret_cast<const uint4*>((warp == 0 ? a.k_step : a.v_step) + (long long)row * a.ldkv +
+                                                      (long long)kv_head * D + lane * 8);
         // Value rows that no copy writes must be finite (their weights are exact zeros; a
         // masked score is replaced whatever its key row holds). Only the sequence's last tile
         // can be short, and only while a buffer has not yet held a whole tile can its rows be
-        // unwritten: the rows past the end of the block's first two tiles are zeroed.
+        // unwritten: the rows past the end of the block's first two tiles are zeroed (the
+        // copies write other rows).
         for (int index = 0; index < 2 && index < tiles; ++index) {
             const int valid = min(TILE, position - (tile_first + index) * TILE + 1);
             for (int chunk = threadIdx.x; chunk < (TILE - valid) * CHUNKS; chunk += THREADS) {
@@ -630,32 +667,15 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
             copy_async_16(q_tile + r * PITCH + c * 8, source, valid);
         }
         copy_async_commit();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        // With the rotation fused the step's own key and value are not in the cache yet: the
-        // block whose last tile holds position `position` computes them, puts them into its
-        // tile and (bit 1) into the cache; the copies leave that row out.
-        const int new_tile = position / TILE;
-        const bool has_new = a.fuse != 0 && tile_first + tiles - 1 == new_tile;
-        uint4 new_raw = make_uint4(0u, 0u, 0u, 0u);          // warp 0: the new key row's chunk, warp 1: the value's
-        if (has_new && warp < 2 && lane < CHUNKS)
-            new_raw = *reinterpret_cast<const uint4*>((warp == 0 ? a.k_step : a.v_step) + (long long)row * a.ldkv +
-                                                      (long long)kv_head * D + lane * 8);
-        auto rows_to_copy = [&](int tile) {
-            return min(TILE, position - tile * TILE + 1) - (a.fuse != 0 && tile == new_tile ? 1 : 0);
-        };
-        issue_tile(k_tiles, v_tiles, a.k_cache, a.v_cache, a.cache, slot, kv_head, tile_first, rows_to_copy(tile_first),
-                   &tile_bar[0]);
         const float scale_log2 = a.scale * LOG2E;
         unsigned q_frag[D / 16][2];                         // Q^T as B operand: (dims, head g)
         for (int index = 0; index < tiles; ++index) {
             const int tile = tile_first + index, buffer = index & 1;
-            if (index + 1 < tiles)                          // the other buffer was read in the step before
-                issue_tile(k_tiles + (buffer ^ 1) * TILE * PITCH, v_tiles + (buffer ^ 1) * TILE * PITCH, a.k_cache,
-                           a.v_cache, a.cache, slot, kv_head, tile + 1, rows_to_copy(tile + 1), &tile_bar[buffer ^ 1]);
             wait_tile(&tile_bar[buffer], (index >> 1) & 1);
             if (index == 0) {
                 copy_async_wait<0>();
+                // The rows zeroed above will be overwritten by later copies: order the two kinds of write.
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncthreads();
                 if (a.fuse & 1) {                           // q as the projection left it: norm, then rotation
                     const int half_lanes = a.rotary_dim / 16;
@@ -767,6 +787,9 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
                 }
             }
             __syncthreads();
+            if (index + 2 < tiles)                          // the buffer that was just read takes the tile after next
+                issue_tile(k_tiles + buffer * TILE * PITCH, v_tiles + buffer * TILE * PITCH, a.k_cache, a.v_cache,
+                           a.cache, slot, kv_head, tile + 2, rows_to_copy(tile + 2), &tile_bar[buffer]);
         }
     }
 #pragma unroll
@@ -779,8 +802,11 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
     // Merge the four warps in warp order through shared memory (the tiles are free now).
     float* merge_out = reinterpret_cast<float*>(k_tiles);                // [4][8][D]
     float* merge_stat = merge_out + 4 * 8 * D;                           // [4][8][2]
-    float* block_out = merge_stat + NARROW_STAT_FLOATS;                  // [8][D]: this block's partial result
-    float* block_stat = block_out + 8 * D;                               // [8][2]
+    // What the other blocks of a cluster send (never used for anything else: a block that is
+    // ahead may send while this one still works on its tiles).
+    float* recv_out = reinterpret_cast<float*>(raw + NARROW_TILE_BYTES);  // [splits][share]
+    float* recv_stat = recv_out + NARROW_RECV_OUT_FLOATS;                // [8 splits][8 heads][2]
+    cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
     __syncthreads();
 #pragma unroll
     for (int n = 0; n < D / 16; ++n) {
@@ -797,29 +823,48 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
         }
     }
     __syncthreads();
-    for (int item = threadIdx.x; item < group * D; item += THREADS) {
-        const int r = item / D, c = item - r * D;
+    // Per head: the block's maximum and denominator and each warp's weight in the merge (a
+    // thread per (head, warp) pair would do; one per head keeps the order of the sums fixed).
+    float* merge_weight = merge_stat + 4 * 8 * 2;                        // [4][8], then [8][2]: maximum, denominator
+    if (threadIdx.x < group) {
+        const int r = threadIdx.x;
         float top = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) top = fmaxf(top, merge_stat[(w * 8 + r) * 2]);
-        float total = 0.f, value = 0.f;
+        float total = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float m = merge_stat[(w * 8 + r) * 2];
             const float factor = m == -INFINITY ? 0.f : exp2f(m - top);
             total += merge_stat[(w * 8 + r) * 2 + 1] * factor;
-            value += merge_out[(w * 8 + r) * D + c] * factor;
+            merge_weight[w * 8 + r] = factor;
         }
+        merge_weight[32 + r * 2] = top;
+        merge_weight[32 + r * 2 + 1] = total;
+        if (CLUSTER && a.splits > 1)                                     // every block of the cluster needs them
+            for (int d = 0; d < a.splits; ++d) {
+                float* stat = cluster.map_shared_rank(recv_stat, d) + (split * 8 + r) * 2;
+                stat[0] = top;
+                stat[1] = total;
+            }
+    }
+    __syncthreads();
+    for (int item = threadIdx.x; item < group * D; item += THREADS) {
+        const int r = item / D, c = item - r * D;
+        const float top = merge_weight[32 + r * 2], total = merge_weight[32 + r * 2 + 1];
+        float value = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) value += merge_out[(w * 8 + r) * D + c] * merge_weight[w * 8 + r];
         const int head = head0 + r;
         if (a.splits == 1) {
             a.out[(long long)row * a.ldo + (long long)head * D + c] =
                 from_float<bf16>(total > 0.f ? value / total : 0.f);
         } else if (CLUSTER) {
-            block_out[r * D + c] = value;
-            if (c == 0) {
-                block_stat[r * 2] = top;
-                block_stat[r * 2 + 1] = total;
-            }
+            // The cluster's blocks share the output elements; this one sends each element of its
+            // partial result to the block that merges it (distributed shared memory).
+            const int share = (group * D + a.splits - 1) / a.splits;
+            const int target = item / share;
+            cluster.map_shared_rank(recv_out, target)[split * share + item - target * share] = value;
         } else {
             const long long where = ((long long)row * a.heads + head) * a.splits + split;
             a.partial_out[where * D + c] = value;
@@ -830,39 +875,28 @@ __global__ void __launch_bounds__(THREADS) attention_decode_narrow_kernel(Args a
         }
     }
     if (CLUSTER && a.splits > 1) {
-        // Every block of the cluster holds its partial result in shared memory; each merges a
-        // share of the output elements, reading the others' partials in split order (so the
-        // result does not depend on timing).
-        cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+        // One barrier: after it every block holds, for its share of the output elements, the
+        // partial values of all splits, and merges them in split order (so the result does not
+        // depend on timing). Nothing is read from another block after the barrier, so a block
+        // may leave as soon as it has written its share.
         cluster.sync();
         const int splits = a.splits;                   // == the cluster's size, <= 8
         const int share = (group * D + splits - 1) / splits;
-        const int begin = split * share, end = min(group * D, begin + share);
-        for (int item = begin + threadIdx.x; item < end; item += THREADS) {
-            const int r = item / D, c = item - r * D;
-            float maxima[8], sums[8], top = -INFINITY;
-#pragma unroll
-            for (int sp = 0; sp < 8; ++sp) {
-                if (sp < splits) {
-                    const float* stat = cluster.map_shared_rank(block_stat, sp);
-                    maxima[sp] = stat[r * 2];
-                    sums[sp] = stat[r * 2 + 1];
-                    top = fmaxf(top, maxima[sp]);
-                }
-            }
+        const int begin = split * share, count = min(group * D, begin + share) - begin;
+        for (int i = threadIdx.x; i < count; i += THREADS) {
+            const int r = (begin + i) / D, c = begin + i - r * D;
+            float top = -INFINITY;
+            for (int sp = 0; sp < splits; ++sp) top = fmaxf(top, recv_stat[(sp * 8 + r) * 2]);
             float total = 0.f, value = 0.f;
-#pragma unroll
-            for (int sp = 0; sp < 8; ++sp) {
-                if (sp < splits) {
-                    const float factor = maxima[sp] == -INFINITY ? 0.f : exp2f(maxima[sp] - top);
-                    total += sums[sp] * factor;
-                    value += cluster.map_shared_rank(block_out, sp)[r * D + c] * factor;
-                }
+            for (int sp = 0; sp < splits; ++sp) {
+                const float m = recv_stat[(sp * 8 + r) * 2];
+                const float factor = m == -INFINITY ? 0.f : exp2f(m - top);
+                total += recv_stat[(sp * 8 + r) * 2 + 1] * factor;
+                value += recv_out[sp * share + i] * factor;
             }
             a.out[(long long)row * a.ldo + (long long)(head0 + r) * D + c] =
                 from_float<bf16>(total > 0.f ? value / total : 0.f);
         }
-        cluster.sync();                                // nobody leaves while its partials are being read
         return;
     }
     if (a.splits > 1 && a.counters) {
@@ -942,13 +976,6 @@ __global__ void attention_combine_kernel(Args a) {
 }
 
 constexpr size_t PREFILL_SHARED = (size_t)(TILE + 4 * TILE) * PITCH * sizeof(bf16);
-constexpr size_t DECODE_TILES = (size_t)(16 + 4 * TILE) * PITCH * sizeof(bf16);
-constexpr size_t DECODE_MERGE = (size_t)16 * PITCH * sizeof(bf16) + (size_t)(4 * 16 * D + 4 * 16 * 2 + 2 * 8 * 32 + 8) * sizeof(float);
-constexpr size_t NARROW_MERGE = (size_t)16 * PITCH * sizeof(bf16) +
-                                (size_t)(4 * 8 * D + NARROW_STAT_FLOATS + 8 * D + 16) * sizeof(float);
-constexpr size_t DECODE_LARGER = DECODE_TILES > DECODE_MERGE ? DECODE_TILES : DECODE_MERGE;
-constexpr size_t DECODE_SHARED = DECODE_LARGER > NARROW_MERGE ? DECODE_LARGER : NARROW_MERGE;
-
 bool aligned(const Args& a) {
     return !((uintptr_t)a.q & 15) && !((uintptr_t)a.k_step & 15) && !((uintptr_t)a.v_step & 15) &&
            !((uintptr_t)a.k_cache & 15) && !((uintptr_t)a.v_cache & 15) && !((uintptr_t)a.out & 3) && !(a.ldq & 7) &&
@@ -1008,18 +1035,18 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
                                                   (int)DECODE_SHARED);
         if (status == cudaSuccess)
             status = cudaFuncSetAttribute(attention_decode_narrow_kernel<false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SHARED);
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NARROW_SHARED);
         if (status == cudaSuccess)
             status = cudaFuncSetAttribute(attention_decode_narrow_kernel<true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SHARED);
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NARROW_SHARED);
         if (status != cudaSuccess) return (int)status;
         configured = true;
     }
     dim3 grid(a.splits, a.kv_heads, a.rows);
     if (clustered)
-        return kidi_launch_clusters(attention_decode_narrow_kernel<true>, grid, THREADS, DECODE_SHARED, stream,
+        return kidi_launch_clusters(attention_decode_narrow_kernel<true>, grid, THREADS, NARROW_SHARED, stream,
                                     (unsigned)a.splits, a);
-    int status = group <= 8 ? kidi_launch(attention_decode_narrow_kernel<false>, grid, THREADS, DECODE_SHARED, stream, a)
+    int status = group <= 8 ? kidi_launch(attention_decode_narrow_kernel<false>, grid, THREADS, NARROW_SHARED, stream, a)
                             : kidi_launch(attention_decode_kernel, grid, THREADS, DECODE_SHARED, stream, a);
     if (status || a.splits == 1 || (group <= 8 && a.counters)) return status;
     dim3 combine(a.heads, a.rows);

@@ -93,9 +93,9 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* _
     // The weights do not depend on the kernel before this one: the first slices are
     // loaded, and the rest of this block's weight rows are asked into L2, before the
     // wait for that kernel; only the batch operand has to wait.
-    pdl_launch_dependents();
 #if !KIDI_SKINNY_HOIST
     pdl_wait();
+    pdl_launch_dependents();
 #endif
     uint4 a[UNROLL][MT][2], b[UNROLL][NT];
 #pragma unroll
@@ -125,6 +125,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* _
 #endif
 #if KIDI_SKINNY_HOIST
     pdl_wait();
+    pdl_launch_dependents();
 #endif
     for (int first = warp; first < slices; first += WARPS * UNROLL) {
 #pragma unroll
