@@ -42,9 +42,6 @@ __device__ __forceinline__ void mbarrier_init(unsigned long long* bar, int count
 __device__ __forceinline__ void mbarrier_expect_tx(unsigned long long* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void mbarrier_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ bool mbarrier_try_wait(unsigned long long* bar, unsigned parity) {
     unsigned done;
     asm volatile(
@@ -139,7 +136,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __shared__ unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
     __shared__ unsigned tmem_base_slot;
     __shared__ int gave_up, is_last;
-    __shared__ float exchange[GATED ? 64 * 17 : 1];       // up rows of one 16-column chunk, padded
+    // The gated epilogue passes the up rows of a 16-column chunk between warps (64 x 17
+    // floats): in the first stage's tile, which is free once the accumulator is complete (a
+    // buffer of its own would leave room for one block per SM instead of two).
+    float* exchange = reinterpret_cast<float*>(tiles);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int feature_tile = blockIdx.x % p.feature_tiles, split = blockIdx.x / p.feature_tiles;

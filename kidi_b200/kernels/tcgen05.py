@@ -24,7 +24,7 @@ from .ops import _check, _need_cuda, _ptr, _stream, c_int, c_longlong, c_void_p,
 
 MAX_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_MAX_ROWS", "64"))
 MIN_FEATURES = 16384                    # the dispatcher uses this kernel for weights at least this tall
-MIN_GATED_ROWS = 17                     # and its fused SiLU gate from this many rows on
+MIN_GATED_ROWS = 9                      # and its fused SiLU gate from this many rows on (below: the skinny kernel)
 WORKSPACE_FLOATS = 8 * 1024 * 1024      # 32 MiB of partial tiles
 COUNTERS = 16384
 
