@@ -115,6 +115,23 @@ __global__ void __launch_bounds__(128) rope_store_kernel(RopeStoreArgs a) {
     }
 }
 
+// Eight consecutive norm weights as 32-bit values (the address is 16-byte aligned: the head
+// width is a multiple of eight).
+__device__ __forceinline__ void load8(const float* p, float (&w)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&w)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 two = __bfloat1622float2(pairs[i]);
+        w[2 * i] = two.x;
+        w[2 * i + 1] = two.y;
+    }
+}
+
 // The same for bfloat16 rows in 16-byte vectors. A (row, head) is handled by a group of
 // L lanes (L the power of two that covers head_dim / 8: 16 lanes for a head of 128), so a
 // warp takes 32 / L of them; lane l of a group owns elements 8l..8l+7 of the head, and its
@@ -127,18 +144,22 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a, i
     const int total_heads = a.heads + 2 * a.kv_heads;
     const int per_warp = 32 / group_lanes;
     const int group = lane / group_lanes, l = lane - group * group_lanes;
-    const long long item = ((long long)blockIdx.x * 4 + warp) * per_warp + group;
+    const int item = (blockIdx.x * 4 + warp) * per_warp + group;   // the launcher keeps the count below 2^31
     // Every lane stays to the end (the shuffles are warp-wide); `alive` says whether the
     // group has a (row, head) to work on.
-    bool alive = item < (long long)a.rows * total_heads;
-    const int row = alive ? (int)(item / total_heads) : 0;
-    const int head = alive ? (int)(item - (long long)row * total_heads) : 0;
-    const int seq = a.row_seq[row];
-    alive = alive && seq >= 0;
-    const int position = a.row_pos[row];
+    bool alive = item < a.rows * total_heads;
+    const int row = alive ? item / total_heads : 0;
+    const int head = alive ? item - row * total_heads : 0;
     const int d = a.head_dim, c0 = 8 * l;
+    bf16* vector = (bf16*)a.qkv + (long long)row * a.ld + head * d;
+    // The row's elements are asked for together with its sequence and position (a padding
+    // row's elements are there to be read; nothing of it is stored).
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (alive && c0 < d) raw = *reinterpret_cast<const uint4*>(vector + c0);
+    const int seq = a.row_seq[row];
+    const int position = a.row_pos[row];
+    alive = alive && seq >= 0;
     const bool mine = alive && c0 < d;
-    bf16* vector = (bf16*)a.qkv + row * a.ld + (long long)head * d;
 
     bf16* cached = nullptr;
     if (alive && head >= a.heads && a.k_cache) {
@@ -154,8 +175,7 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a, i
                      cache_row_offset(a.cache, a.seq_slot[seq], position, kv_head);
         }
     }
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (mine) raw = *reinterpret_cast<const uint4*>(vector + c0);
+    if (!mine) raw = make_uint4(0u, 0u, 0u, 0u);
     const bool plain = head >= a.heads + a.kv_heads || !a.transform;  // a value head, or copy only
     if (plain && cached && mine) *reinterpret_cast<uint4*>(cached + c0) = raw;
     const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -175,8 +195,10 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a, i
             square += __shfl_xor_sync(0xffffffffu, square, offset);
         if (weight && mine && !plain) {
             const float inv = 1.0f / sqrtf(square / (float)d + a.eps);
+            float w[8];
+            load8(weight + c0, w);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * to_float(weight[c0 + i]);
+            for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * w[i];
         }
     }
     if (a.cos_table) {
@@ -213,7 +235,8 @@ KIDI_API int kidi_rope_store(const RopeStoreArgs* args, int dtype, int norm_dtyp
     if (a.head_dim > 256 || a.head_dim <= 0 || a.rotary_dim > a.head_dim || (a.rotary_dim & 1)) return KIDI_REFUSED_SIZE;
     const long long items = (long long)a.rows * (a.heads + 2 * a.kv_heads);
     const unsigned blocks = (unsigned)((items + 3) / 4);
-    const bool vectors = dtype == KIDI_BF16 && !(a.head_dim & 7) && !(a.ld & 7) && !((uintptr_t)a.qkv & 15) &&
+    const bool vectors = dtype == KIDI_BF16 && items < (1LL << 30) && !((uintptr_t)a.q_norm & 15) &&
+                         !((uintptr_t)a.k_norm & 15) && !(a.head_dim & 7) && !(a.ld & 7) && !((uintptr_t)a.qkv & 15) &&
                          !((uintptr_t)a.k_cache & 15) && !((uintptr_t)a.v_cache & 15) &&
                          (!a.cos_table || (!(a.rotary_dim & 15) && !((uintptr_t)a.cos_table & 15) &&
                                            !((uintptr_t)a.sin_table & 15)));

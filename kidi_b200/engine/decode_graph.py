@@ -69,12 +69,13 @@ class DecodeSession:
             tokens=rows * 0, row_seq=rows, row_pos=rows * 0, seq_slot=rows * 0, seq_start=rows * 0,
             seq_len=rows * 0 + 1, seq_row0=rows, want_rows=rows)
         self._context = StepContext(self._plan, self.tables, engine.cache, engine.dtype, device, engine._workspaces)
-        heads = _widest_decode(engine)
-        if heads is not None:
+        widest = _widest_decode(engine)
+        if widest is not None:
             # The number of key splits is a launch dimension: it is fixed when the graph is
             # captured, from the longest sequence this session may come to hold.
+            heads, head_dim = widest
             self._context.decode_splits = attention_kernels.decode_splits(
-                capacity, heads, self._plan.max_total, device)
+                capacity, heads, self._plan.max_total, device, head_dim)
         self._stream = torch.cuda.Stream(device=device)
 
     # ------------------------------------------------------------------ set-up
@@ -202,8 +203,9 @@ class DecodeSession:
         return self._selected_host_view[:self.live].tolist()
 
 
-def _widest_decode(engine) -> Optional[int]:
-    """The key/value head count that decides how decode attention is split (None when
-    no layer has an attention cache)."""
-    heads = [group.request.kv_heads for group in engine.cache.kv_groups]
-    return min(heads) if heads else None
+def _widest_decode(engine):
+    """The (key/value head count, head width) that decides how decode attention is split:
+    those of the attention cache with the fewest key/value heads (None when no layer has
+    an attention cache)."""
+    shapes = [(group.request.kv_heads, group.request.head_dim) for group in engine.cache.kv_groups]
+    return min(shapes) if shapes else None

@@ -120,12 +120,19 @@ def sm_count(device: torch.device) -> int:
     return _sm_count[index]
 
 
-BLOCKS_PER_SM = 3          # decode attention blocks that fit one SM (shared memory)
+def blocks_per_sm(head_dim: int = 128) -> int:
+    """Decode attention blocks that fit one SM: 8 query rows and four 64-row tiles with rows
+    padded by 8 elements, plus what a cluster's blocks send each other; at most four by
+    registers. Three at head width 128."""
+    block = (8 + 4 * 64) * (head_dim + 8) * 2 + (8 * head_dim + 8 + 128) * 4 + 1024
+    return max(1, min(4, (228 * 1024) // block))
+
+
 FIXED_COST_TILES = 6.0     # what a block spends beside its tiles (launch, query, merge of splits), in tile times;
                            # fitted to step times measured on a B200 at batch 1, 8 and 64
 
 
-def decode_splits(rows: int, kv_heads: int, longest: int, device: torch.device) -> int:
+def decode_splits(rows: int, kv_heads: int, longest: int, device: torch.device, head_dim: int = 128) -> int:
     """How many blocks share a sequence's keys. A block walks its 64-key pages one after
     another, so the kernel's time is (waves of blocks) x (pages per block + a fixed cost);
     the number of splits that makes this smallest is chosen, at most one per page."""
@@ -133,7 +140,7 @@ def decode_splits(rows: int, kv_heads: int, longest: int, device: torch.device) 
     forced = int(os.environ.get("KIDI_B200_DECODE_SPLITS", "0"))
     if forced:
         return max(1, min(pages, forced))
-    slots = BLOCKS_PER_SM * sm_count(device)
+    slots = blocks_per_sm(head_dim) * sm_count(device)
     items = max(1, rows * kv_heads)
     best, best_cost = 1, None
     for splits in range(1, min(pages, 32) + 1):
@@ -191,13 +198,14 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
     stream = ops._stream()
     if decode:
         longest = min(plan.max_total, int(window)) + 64 if window else plan.max_total
-        splits = getattr(ctx, "decode_splits", None) or decode_splits(qkv.shape[0], kv_heads, longest, qkv.device)
+        splits = getattr(ctx, "decode_splits", None) or decode_splits(qkv.shape[0], kv_heads, longest, qkv.device,
+                                                                       head_dim)
         # One wave of blocks and few splits: the blocks of a (row, key/value head) form a
         # thread-block cluster and merge through distributed shared memory (measured 13.5
         # against 17.1 us a layer at batch 8). Clusters that must wait for several free slots of
         # one GPC at once lose that again when the grid takes more than a wave (70.6 against
         # 67.0 us at batch 64).
-        one_wave = qkv.shape[0] * kv_heads * splits <= BLOCKS_PER_SM * sm_count(qkv.device)
+        one_wave = qkv.shape[0] * kv_heads * splits <= blocks_per_sm(head_dim) * sm_count(qkv.device)
         clustered = 1 < splits <= CLUSTER_SPLITS and heads // kv_heads <= 8 and one_wave
         if splits > 1 and not clustered:
             workspace = ctx.workspace("attention_partial", qkv.shape[0] * heads * splits * (head_dim + 2))

@@ -27,6 +27,7 @@ LENGTHS = {
     "tiny_b": [1, 7, 17, 31, 66, 129, 200, 256],
     "tiny_c": [2, 40, 71, 141, 250, 320],
     "tiny_d": [3, 127, 128, 129, 300, 420],
+    "tiny_e": [1, 130, 257, 384],
 }
 
 

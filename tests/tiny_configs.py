@@ -47,4 +47,13 @@ TINY_D = {
     "sliding_window": 150,
 }
 
-ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
+# One layer, 2 heads over one key/value head, head width 128 (the benchmark model's width:
+# its attention kernels, whole-model), full attention, untied head.
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu",
+    "num_hidden_layers": 1, "hidden_size": 160, "num_attention_heads": 2, "num_key_value_heads": 1,
+    "head_dim": 128, "intermediate_size": 168, "vocab_size": 307, "rope_theta": 300000.0,
+    "rms_norm_eps": 5e-6, "tie_word_embeddings": False, "max_position_embeddings": 384,
+}
+
+ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D, "tiny_e": TINY_E}
