@@ -128,8 +128,11 @@ def blocks_per_sm(head_dim: int = 128) -> int:
     return max(1, min(4, (228 * 1024) // block))
 
 
-FIXED_COST_TILES = 6.0     # what a block spends beside its tiles (launch, query, merge of splits), in tile times;
-                           # fitted to step times measured on a B200 at batch 1, 8 and 64
+# What a block spends beside its tiles (launch, tables, query, merge of the splits), in tile
+# times, fitted to kernel times measured on a B200 (batch 1 to 64, 300 to 16,000 tokens): less
+# when the splits merge inside a thread-block cluster than through a workspace.
+FIXED_COST_TILES = 6.5
+FIXED_COST_TILES_CLUSTER = 3.5
 
 
 def decode_splits(rows: int, kv_heads: int, longest: int, device: torch.device, head_dim: int = 128) -> int:
@@ -144,7 +147,9 @@ def decode_splits(rows: int, kv_heads: int, longest: int, device: torch.device, 
     items = max(1, rows * kv_heads)
     best, best_cost = 1, None
     for splits in range(1, min(pages, 32) + 1):
-        cost = -(-items * splits // slots) * (-(-pages // splits) + FIXED_COST_TILES)
+        clustered = 1 < splits <= CLUSTER_SPLITS and items * splits <= slots
+        fixed = FIXED_COST_TILES_CLUSTER if clustered else FIXED_COST_TILES
+        cost = -(-items * splits // slots) * (-(-pages // splits) + fixed)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = splits, cost
     return best
