@@ -97,7 +97,8 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // (Letting dependents start before the wait makes a whole chain of future kernels resident
 // at once; they take the slots that the later waves of the running kernel need: measured
 // 5.5 against 3.9 ms per decode step. In this order the replayed decode graph still loses
-// 2% against ordinary launches, 3.75 against 3.66 ms, so the switch stays off.)
+// 2% against ordinary launches, 3.75 against 3.66 ms, and 4% when only the weight-streaming
+// products start early, 3.80 against 3.65 ms, so the switch stays off.)
 __device__ __forceinline__ void pdl_prologue() {
     pdl_wait();
     pdl_launch_dependents();
