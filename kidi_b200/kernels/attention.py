@@ -24,6 +24,9 @@ FUSED_MERGE = os.environ.get("KIDI_B200_FUSED_MERGE", "1") == "1"
 # One token per sequence: the decode kernel normalises and rotates q and the new key itself and
 # writes the new key and value to the cache (one kernel less per layer); 0 switches that off.
 FUSE_ROTATION = os.environ.get("KIDI_B200_FUSE_ROTATION", "1") == "1"
+# Head widths that are multiples of 64: the decode kernel takes whole pages by TMA tensor copies
+# (0: row by row into padded tiles, as for the other widths).
+DECODE_SWIZZLED = os.environ.get("KIDI_B200_DECODE_SWIZZLED", "1") == "1"
 # Up to this many splits merge inside a thread-block cluster (no workspace, no second kernel);
 # 0 switches that off.
 CLUSTER_SPLITS = int(os.environ.get("KIDI_B200_CLUSTER_SPLITS", "8"))
@@ -40,7 +43,7 @@ class FastAttentionArgs(ctypes.Structure):
                 ("scale", c_float), ("partial_out", c_void_p), ("partial_stat", c_void_p), ("splits", c_int),
                 ("counters", c_void_p), ("fuse", c_int), ("norm_is_float", c_int), ("q_norm", c_void_p),
                 ("k_norm", c_void_p), ("cos_table", c_void_p), ("sin_table", c_void_p), ("rotary_dim", c_int),
-                ("eps", c_float)]
+                ("eps", c_float), ("cache_rows", c_longlong)]
 
 
 _libraries: Dict[int, ctypes.CDLL] = {}
@@ -56,6 +59,9 @@ def library(head_dim: int) -> ctypes.CDLL:
         lib.kidi_attention_prefill.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_attention_decode.argtypes = [c_void_p, c_void_p]
         lib.kidi_attention_prefill.restype = lib.kidi_attention_decode.restype = c_int
+        lib.kidi_attention_decode_swizzled.argtypes = [c_int]
+        lib.kidi_attention_decode_swizzled.restype = None
+        lib.kidi_attention_decode_swizzled(1 if DECODE_SWIZZLED else 0)
         ops.configure_library(lib)
         _libraries[head_dim] = lib
     return lib
@@ -223,6 +229,7 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
                 # Zeroed when it is made; the kernel leaves every counter at zero.
                 args.counters = ctx.workspace("attention_counters", qkv.shape[0] * kv_heads, zero=True).data_ptr()
         args.splits = splits
+        args.cache_rows = kv_view.keys.numel() // head_dim if kv_view.keys.is_contiguous() else 0
         if rotation is not None:
             item = qkv.element_size()
             args.k_step = qkv.data_ptr() + heads * head_dim * item
