@@ -357,7 +357,8 @@ def test_attention_over_cache(kind, dtype, geometry):
 
 
 @pytest.mark.parametrize("kind,dtype", [("generic", torch.float32), ("tensor_core", torch.bfloat16)])
-@pytest.mark.parametrize("geometry", [(8, 2, 128, None), (6, 6, 48, None), (16, 1, 32, 90), (4, 2, 64, 64)])
+@pytest.mark.parametrize("geometry", [(8, 2, 128, None), (6, 6, 48, None), (16, 1, 32, 90), (4, 2, 64, 64),
+                                      (4, 2, 256, None), (3, 1, 192, 100)])
 @pytest.mark.parametrize("splits", [1, 3, 40])
 def test_attention_decode(kind, dtype, geometry, splits):
     """One token per sequence against caches of very different lengths, with the key
@@ -480,7 +481,7 @@ def test_attention_prompts_tensor_memory(geometry):
 
 
 @pytest.mark.parametrize("geometry", [(8, 2, 128, None, 128), (6, 6, 48, None, 32), (16, 2, 64, 90, 64),
-                                      (4, 1, 32, None, 0)])
+                                      (4, 1, 32, None, 0), (2, 1, 256, None, 64), (6, 2, 192, 70, 192)])
 @pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("norm_dtype", [torch.bfloat16, torch.float32])
 def test_decode_with_the_rotation_inside(geometry, splits, norm_dtype):
