@@ -216,11 +216,18 @@ struct Params {
     const int* seq_row0;    // [seqs] first packed row
     int heads, kv_heads, window;
     float scale;
+    // Prompts that continue sequences whose earlier tokens are in the cache (from_cache): every
+    // key and value, the step's own included, is read from the cache's pages (the step's rows
+    // were written there before this kernel), two 64-token pages per tile.
+    int from_cache;
+    const int* seq_start;   // [seqs] tokens in the cache before this step
+    const int* seq_slot;    // [seqs]
+    CacheGeometry cache;
 };
 
 // Where a block works: its sequence, query rows, heads and key tiles.
 struct Place {
-    int count, q0, row0, q_rows, tile_low, tiles, kv_head, head0, heads_here;
+    int count, q0, row0, q_rows, tile_low, tiles, kv_head, head0, heads_here, start, slot;
     __device__ __forceinline__ explicit Place(const Params& p) {
         // Long blocks first: a block's number of key tiles grows with its query tile, and blocks
         // start in the order of their linear index, of which z is the slowest part.
@@ -234,9 +241,11 @@ struct Place {
         count = p.seq_len[seq];
         q0 = q_index * BM;
         row0 = p.seq_row0[seq];
+        start = p.from_cache ? p.seq_start[seq] : 0;
+        slot = p.from_cache ? p.seq_slot[seq] : 0;
         q_rows = min(BM, count - q0);
-        const int high = q0 + q_rows - 1;                                  // last query position of the block
-        const int low = p.window > 0 ? max(0, q0 - p.window + 1) : 0;     // first key any of its queries sees
+        const int high = start + q0 + q_rows - 1;                          // last query position of the block
+        const int low = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;   // first key any of its queries sees
         tile_low = low / BN;
         tiles = high / BN - tile_low + 1;
     }
@@ -289,7 +298,8 @@ __device__ __forceinline__ void store_probabilities(const unsigned (&packed)[SHA
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
-attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map, Params p) {
+attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map, const __grid_constant__ CUtensorMap k_map,
+                                 const __grid_constant__ CUtensorMap v_map, Params p) {
     // All shared memory is dynamic and laid out here; the tiles come first because the
     // 128-byte swizzle wants them on 1024-byte boundaries.
     extern __shared__ __align__(1024) unsigned char base[];
@@ -406,13 +416,27 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map, Params
                 auto load_tile = [&](unsigned char* tile, unsigned long long* bar, int column, int row) {
                     for (int s = 0; s < SPANS; ++s) tma_load_2d(tile + s * SPAN_BYTES, &map, bar, column + 64 * s, row);
                 };
+                // From the cache a tile is two pages (64 rows each) of the sequence's row of the block
+                // table; a page past the sequence's last one is replaced by the last one (masked).
+                const int last_page = (at.start + at.count - 1) >> 6;
+                auto load_pages = [&](unsigned char* tile, unsigned long long* bar, const CUtensorMap* pages, int j) {
+                    for (int half = 0; half < 2; ++half) {
+                        const int page_index = min((tile_low + j) * 2 + half, last_page);
+                        const int page = p.cache.table[(long long)at.slot * p.cache.pages_per_seq + page_index];
+                        const int page_row = (page * p.cache.kv_heads + at.kv_head) * 64;
+                        for (int s = 0; s < SPANS; ++s)
+                            tma_load_2d(tile + s * SPAN_BYTES + half * (64 * 128), pages, bar, 64 * s, page_row);
+                    }
+                };
                 auto load_k = [&](int j) {
                     mbarrier_expect_tx(&ctl.k_full, QKV_TILE);
-                    load_tile(k_tile, &ctl.k_full, k_col, row0 + (tile_low + j) * BN);
+                    if (p.from_cache) load_pages(k_tile, &ctl.k_full, &k_map, j);
+                    else load_tile(k_tile, &ctl.k_full, k_col, row0 + (tile_low + j) * BN);
                 };
                 auto load_v = [&](int j) {
                     mbarrier_expect_tx(&ctl.v_full[j & 1], QKV_TILE);
-                    load_tile(v_tiles + (j & 1) * QKV_TILE, &ctl.v_full[j & 1], v_col, row0 + (tile_low + j) * BN);
+                    if (p.from_cache) load_pages(v_tiles + (j & 1) * QKV_TILE, &ctl.v_full[j & 1], &v_map, j);
+                    else load_tile(v_tiles + (j & 1) * QKV_TILE, &ctl.v_full[j & 1], v_col, row0 + (tile_low + j) * BN);
                 };
                 mbarrier_expect_tx(&ctl.q_full, heads_here * QKV_TILE);
                 for (int h = 0; h < heads_here; ++h)
@@ -446,7 +470,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map, Params
             const int group = ((warp - CONTROL_WARPS) >> 2) % GROUPS;   // which share of a tile's keys
             const int r = quarter * 32 + lane;                      // query row of this thread
             const int key = group * SHARE;                          // its first key within a tile
-            const int position = q0 + r;
+            const int position = at.start + q0 + r;
             const unsigned lane_bits = (unsigned)(quarter * 32) << 16;
             const unsigned tmem_s = tmem + h * 128 + lane_bits + key, tmem_o = tmem + 256 + h * 128 + lane_bits;
             unsigned char* p_tile = p_tiles + h * P_TILE;
@@ -469,7 +493,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map, Params
                 const int key0 = (tile_low + j) * BN;
                 const int last = position - key0 - key;
                 const int first = p.window > 0 ? position - p.window + 1 - key0 - key : 0;
-                const bool masked = key0 + BN - 1 > q0 || (p.window > 0 && q0 + BM - p.window > key0);
+                const bool masked =
+                    key0 + BN - 1 > at.start + q0 || (p.window > 0 && at.start + q0 + BM - p.window > key0);
                 ok = mbarrier_wait(&ctl.s_ready[h], j & 1, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -614,9 +639,23 @@ KIDI_API int kidi_attention_tcgen05_timeout_flag() {
 // Attention of every row of a step whose sequences all start at position 0.
 // qkv [rows, ld]: heads query heads, then kv_heads key heads, then kv_heads value heads,
 // each D wide, bfloat16, 16-byte aligned rows. out [rows, ldo] bfloat16.
+struct KidiPromptCache {     // where the keys and values lie when prompts continue cached sequences
+    const void* keys;        // [pages, kv_heads, 64, D] bfloat16
+    const void* values;
+    long long rows;          // pages * kv_heads * 64
+    const int* table;        // [slots, pages_per_seq]
+    int pages_per_seq;
+    const int* seq_start;    // [seqs]
+    const int* seq_slot;     // [seqs]
+};
+
+// `cache` null: every sequence starts at position 0 and its keys are rows of qkv. Else every
+// key and value is read from the cache (64-token pages; no ring), into which the step's own
+// rows have been written already.
 KIDI_API int kidi_attention_prefill_tcgen05(const void* qkv, long long ld, int rows, void* out, long long ldo,
                                             const int* seq_len, const int* seq_row0, int seqs, int max_new, int heads,
-                                            int kv_heads, int window, float scale, cudaStream_t stream) {
+                                            int kv_heads, int window, float scale, const KidiPromptCache* cache,
+                                            cudaStream_t stream) {
     if (rows <= 0 || seqs <= 0 || max_new <= 0) return 0;
     if (!(scale > 0.f) || heads % kv_heads || (max_new + BM - 1) / BM > 65535 || seqs > 65535 || (ld & 7) ||
         (ldo & 7) || ((uintptr_t)qkv & 15) ||
@@ -642,7 +681,34 @@ KIDI_API int kidi_attention_prefill_tcgen05(const void* qkv, long long ld, int r
         if (status != cudaSuccess) return (int)status;
         configured[device] = true;
     }
+    CUtensorMap k_map, v_map;
+    memset(&k_map, 0, sizeof(k_map));
+    memset(&v_map, 0, sizeof(v_map));
     Params p;
+    memset(&p, 0, sizeof(p));
+    if (cache) {
+        if (!cache->keys || !cache->values || cache->rows <= 0 || !cache->table || !cache->seq_start ||
+            !cache->seq_slot || ((uintptr_t)cache->keys & 15) || ((uintptr_t)cache->values & 15))
+            return KIDI_REFUSED_SIZE;
+        const cuuint64_t page_dims[2] = {(cuuint64_t)D, (cuuint64_t)cache->rows};
+        const cuuint64_t page_strides[1] = {(cuuint64_t)D * 2};
+        const cuuint32_t page_box[2] = {64, 64};
+        const void* bases[2] = {cache->keys, cache->values};
+        CUtensorMap* maps[2] = {&k_map, &v_map};
+        for (int i = 0; i < 2; ++i)
+            if (encode(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(bases[i]), page_dims,
+                       page_strides, page_box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return KIDI_REFUSED_SIZE;
+        p.from_cache = 1;
+        p.seq_start = cache->seq_start;
+        p.seq_slot = cache->seq_slot;
+        p.cache.table = cache->table;
+        p.cache.pages_per_seq = cache->pages_per_seq;
+        p.cache.page_shift = 6;
+        p.cache.kv_heads = kv_heads;
+        p.cache.head_dim = D;
+    }
     p.out = (bf16*)out;
     p.ldo = ldo;
     p.seq_len = seq_len;
@@ -653,6 +719,6 @@ KIDI_API int kidi_attention_prefill_tcgen05(const void* qkv, long long ld, int r
     p.scale = scale;
     const int group_size = heads / kv_heads;
     dim3 grid(kv_heads * ((group_size + HEADS - 1) / HEADS), seqs, (max_new + BM - 1) / BM);
-    attention_prefill_tcgen05_kernel<<<grid, THREADS, SHARED_BYTES, stream>>>(map, p);
+    attention_prefill_tcgen05_kernel<<<grid, THREADS, SHARED_BYTES, stream>>>(map, k_map, v_map, p);
     return kidi_launch_status();
 }

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
@@ -74,7 +74,7 @@ def tensor_memory_library(head_dim: int) -> ctypes.CDLL:
         lib = load_library(f"attention_tcgen05_d{head_dim}", ("attention_tcgen05.cu",), {"KIDI_HEAD_DIM": head_dim})
         lib.kidi_attention_prefill_tcgen05.argtypes = [
             c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-            c_float, c_void_p]
+            c_float, c_void_p, c_void_p]
         lib.kidi_attention_prefill_tcgen05.restype = c_int
         lib.kidi_attention_tcgen05_timeout_flag.restype = c_int
         ops.configure_library(lib)
@@ -91,14 +91,29 @@ def tensor_memory_fits(qkv: torch.Tensor, out: torch.Tensor, head_dim: int, head
             and qkv.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
+class PromptCache(ctypes.Structure):
+    """Where the keys and values lie when prompts continue cached sequences (KidiPromptCache)."""
+    _fields_ = [("keys", c_void_p), ("values", c_void_p), ("rows", c_longlong), ("table", c_void_p),
+                ("pages_per_seq", c_int), ("seq_start", c_void_p), ("seq_slot", c_void_p)]
+
+
 def prefill_tensor_memory(qkv: torch.Tensor, out: torch.Tensor, seq_len: torch.Tensor, seq_row0: torch.Tensor,
                           seqs: int, max_new: int, *, heads: int, kv_heads: int, head_dim: int, scale: float,
-                          window: int) -> None:
-    """Causal attention of packed prompts that start at position 0 (every key is a row of qkv)."""
+                          window: int, kv_view=None, seq_start: Optional[torch.Tensor] = None,
+                          seq_slot: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of packed prompts. Without `kv_view` the prompts start at position 0
+    and every key is a row of qkv; with it (a cache of 64-token pages without a ring, into
+    which the step's rows have been written) every key and value is read from the cache,
+    so the prompts may continue sequences of `seq_start` tokens."""
     lib = tensor_memory_library(head_dim)
+    cache = None
+    if kv_view is not None:
+        cache = PromptCache(kv_view.keys.data_ptr(), kv_view.values.data_ptr(), kv_view.keys.numel() // head_dim,
+                            kv_view.table.data_ptr(), kv_view.table.shape[1], seq_start.data_ptr(), seq_slot.data_ptr())
     _check(lib.kidi_attention_prefill_tcgen05(
         qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), out.stride(0), seq_len.data_ptr(),
-        seq_row0.data_ptr(), seqs, max_new, heads, kv_heads, int(window or 0), float(scale), ops._stream()),
+        seq_row0.data_ptr(), seqs, max_new, heads, kv_heads, int(window or 0), float(scale),
+        ctypes.byref(cache) if cache is not None else None, ops._stream()),
         "attention_prefill_tcgen05")
 
 
@@ -180,21 +195,32 @@ def fuses_rotation(plan, qkv: torch.Tensor, *, heads: int, kv_heads: int, head_d
     return True
 
 
-def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step, rotation=None) -> None:
-    """`rotation` (only where `fuses_rotation` said yes): dict(q_norm, k_norm, eps, cos, sin,
-    rotary_dim, store): the kernel normalises and rotates q and the step's key and, with
-    `store`, writes the step's key and value to the cache."""
+def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step, rotation=None,
+        step_rows_cached: bool = False) -> None:
+    """`keys_in_step`: the step's own keys and values are read from qkv (else from the
+    cache, like the earlier ones). `step_rows_cached`: they are in the cache as well (a cache
+    that keeps every page is written before attention), so a kernel may read everything
+    from there. `rotation` (only where `fuses_rotation` said yes): dict(q_norm, k_norm, eps,
+    cos, sin, rotary_dim, store): the kernel normalises and rotates q and the step's key
+    and, with `store`, writes the step's key and value to the cache."""
     plan, tables = ctx.plan, ctx.tables
     decode = plan.is_decode and not keys_in_step
     if not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode) or (kv_view is not None and kv_view.page_size != 64):
         ops.attention_generic(qkv, out, heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale,
                               window=window, tables=tables, kv_view=kv_view, keys_in_step=keys_in_step)
         return
-    if (not decode and keys_in_step and int(plan.seq_start.max()) == 0
-            and tensor_memory_fits(qkv, out, head_dim, heads, kv_heads, scale)):
-        prefill_tensor_memory(qkv, out, tables.seq_len, tables.seq_row0, plan.n_seqs, plan.max_new, heads=heads,
-                              kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
-        return
+    if not decode and tensor_memory_fits(qkv, out, head_dim, heads, kv_heads, scale):
+        common = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
+        if keys_in_step and int(plan.seq_start.max()) == 0:      # every key is a row of this step
+            prefill_tensor_memory(qkv, out, tables.seq_len, tables.seq_row0, plan.n_seqs, plan.max_new, **common)
+            return
+        # Prompts that continue cached sequences: the step's rows are in the cache already (a
+        # cache that keeps every page is written before attention), so every key comes from there.
+        if (kv_view is not None and (step_rows_cached or not keys_in_step) and kv_view.ring_pages == 0
+                and kv_view.page_size == 64 and kv_view.keys.is_contiguous() and kv_view.table.is_contiguous()):
+            prefill_tensor_memory(qkv, out, tables.seq_len, tables.seq_row0, plan.n_seqs, plan.max_new, kv_view=kv_view,
+                                  seq_start=tables.seq_start, seq_slot=tables.seq_slot, **common)
+            return
     item = qkv.element_size()
     args = FastAttentionArgs(
         qkv.data_ptr(), qkv.stride(0),

@@ -107,7 +107,8 @@ class Attention(Part):
         keys_in_step = owns_cache and not plan.is_decode
         rotation = dict(q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, store=True, **rotate) if fused else None
         ctx.attention(qkv, attended, scale=self.scale, window=self.window, kv_view=view,
-                      keys_in_step=keys_in_step, rotation=rotation, **common)
+                      keys_in_step=keys_in_step, rotation=rotation, step_rows_cached=store_first and not fused,
+                      **common)
         if owns_cache and not store_first:
             ops.rope_store(qkv, q_norm=None, k_norm=None, eps=self.eps, tables=ctx.tables, kv_view=view, store=True,
                            transform=False, cos=None, sin=None, rotary_dim=0, **common)

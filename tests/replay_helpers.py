@@ -32,6 +32,33 @@ def run_whole(engine, requests) -> Dict[str, np.ndarray]:
     return out
 
 
+def run_chunked(engine, requests, chunk: int, batch_size: int = 2) -> Dict[str, np.ndarray]:
+    """Batches of requests whose prompts come in chunks of `chunk` tokens: every step but the
+    first continues sequences that the cache already holds, with several tokens each (a
+    request that has run out brings nothing more and leaves the steps)."""
+    out = {}
+    names = list(requests)
+    for begin in range(0, len(names), batch_size):
+        batch = names[begin:begin + batch_size]
+        slots = {name: engine.acquire() for name in batch}
+        rows = {name: [] for name in batch}
+        done = {name: 0 for name in batch}
+        while any(done[name] < len(requests[name]) for name in batch):
+            live = [name for name in batch if done[name] < len(requests[name])]
+            pieces = [requests[name][done[name]:done[name] + chunk] for name in live]
+            logits = engine.step(StepBatch([slots[name] for name in live], pieces,
+                                           [list(range(len(piece))) for piece in pieces])).cpu().numpy()
+            cursor = 0
+            for name, piece in zip(live, pieces):
+                rows[name].append(logits[cursor:cursor + len(piece)])
+                cursor += len(piece)
+                done[name] += len(piece)
+        for name in batch:
+            out[name] = np.concatenate(rows[name], axis=0)
+            engine.release(slots[name])
+    return out
+
+
 def run_tail_decoded(engine, requests, tail: int = 32) -> Dict[str, np.ndarray]:
     """Each request alone: all but the last `tail` tokens in one step, the rest one by one."""
     out = {}

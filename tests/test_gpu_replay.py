@@ -86,6 +86,20 @@ def test_unequal_batches_with_slot_reuse(model_folders, references, name, dtype)
     rh.assert_matches(found, expected, tolerance(dtype), f"{name} {dtype} batches of 2, reversed")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(ALL))
+def test_prompts_in_chunks(model_folders, references, name, dtype):
+    """Prompts fed 100 tokens at a time, two requests a batch: steps of several tokens that
+    continue what the cache holds (pages, rings and the tensor-memory attention kernel's
+    reading from the cache all meet a chunk boundary inside a page)."""
+    requests, expected = references[name]
+    engine = make_engine(model_folders[name], dtype)
+    rh.assert_matches(rh.run_chunked(engine, requests, chunk=100), expected, tolerance(dtype),
+                      f"{name} {dtype} in chunks of 100")
+    engine.cache.check()
+    assert not engine.cache.slots.held
+
+
 @pytest.mark.parametrize("name", list(ALL))
 def test_cuts_agree_in_32_bit(model_folders, references, name):
     """In 32-bit the logits of a position do not depend on the cut at all: the kernels
