@@ -46,11 +46,14 @@ def test_greedy_generation_matches_the_plain_model_in_32_bit(model_folders, name
     assert not engine.cache.slots.held
 
 
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d", "tiny_e"])
 def test_greedy_generation_in_bfloat16(model_folders, name):
     config, tensors = plain_model.read_model_folder(model_folders[name])
     generator = np.random.default_rng(5)
-    prompts = [generator.integers(0, config["vocab_size"], size=n).tolist() for n in [3, 17, 40, 8]]
+    # Head widths 64 and 128 (tiny_d, tiny_e) take the tensor-memory prompt kernel and the
+    # page-copy decode kernel: prompts longer than one of their tiles.
+    lengths = [3, 17, 40, 8] if name in ("tiny_a", "tiny_b") else [3, 140, 200, 64]
+    prompts = [generator.integers(0, config["vocab_size"], size=n).tolist() for n in lengths]
     engine = load(model_folders[name], "bfloat16", max_tokens=1024)
     found = engine.generate(prompts, max_new_tokens=12, ignore_eos=True)
     eager = engine.generate(prompts, max_new_tokens=12, ignore_eos=True, use_graph=False)
