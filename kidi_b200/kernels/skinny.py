@@ -74,7 +74,8 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Opt
     return out
 
 
-def gemm_silu_gate(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemm_silu_gate(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+                   row_tiles: int = 0) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) for weight = [Wg; Wu] of shape [2I, K]."""
     _need_cuda(x, weight)
     if not supports(x, weight) or x.shape[1] != weight.shape[1] or weight.shape[0] % 2:
@@ -84,6 +85,6 @@ def gemm_silu_gate(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Te
     if out is None:
         out = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
     _check(_library().kidi_gemm_skinny(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), M, inter, K,
-                                       x.stride(0), weight.stride(0), out.stride(0), 1, 2, _stream()),
+                                       x.stride(0), weight.stride(0), out.stride(0), 1, row_tiles, _stream()),
            "gemm_silu_gate")
     return out
