@@ -59,7 +59,10 @@ constexpr size_t NARROW_SHARED = NARROW_TILE_BYTES + NARROW_RECV_FLOATS * sizeof
 // warps' partial results reuse the tiles).
 constexpr size_t SWIZZLED_TILE_BYTES = ((size_t)(4 * TILE * D + 8 * PITCH) * sizeof(bf16) + 15) / 16 * 16;
 constexpr size_t SWIZZLED_SHARED = 1024 + SWIZZLED_TILE_BYTES + NARROW_RECV_FLOATS * sizeof(float);
-static_assert((size_t)(4 * 8 * D + 4 * 8 * 2 + 2 * 8 * 32 + 8) * sizeof(float) <= (size_t)4 * TILE * D * sizeof(bf16) || D % 64,
+// The ring form of it: three tiles.
+constexpr size_t RING_TILE_BYTES = ((size_t)(3 * TILE * D + 8 * PITCH) * sizeof(bf16) + 15) / 16 * 16;
+constexpr size_t RING_SHARED = 1024 + RING_TILE_BYTES + NARROW_RECV_FLOATS * sizeof(float);
+static_assert((size_t)(4 * 8 * D + 4 * 8 * 2 + 2 * 8 * 32 + 8) * sizeof(float) <= (size_t)3 * TILE * D * sizeof(bf16) || D % 64,
               "the warps' partial results fit the tiles");
 
 __device__ __forceinline__ unsigned smem_address(const void* pointer) {
@@ -611,15 +614,17 @@ __device__ __forceinline__ float head_square_sum(uint4 own) {
 // reach 5.7 TB/s. A page is copied whole: rows past the sequence's end hold what the
 // cache held before (zeros or an earlier sequence's finite values), and their weights
 // are exact zeros.
-template <bool CLUSTER, bool SWIZZLED>
+template <bool CLUSTER, int FORM>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                                Args a) {
+    constexpr bool SWIZZLED = FORM != 0, RING = FORM == 2;
+    constexpr int BUFFERS = RING ? 3 : 4;
     extern __shared__ __align__(16) unsigned char raw_unaligned[];
     // Swizzled tiles want 1024-byte boundaries and come first; the query rows follow them.
     unsigned char* raw = SWIZZLED ? (unsigned char*)(((uintptr_t)raw_unaligned + 1023) & ~(uintptr_t)1023) : raw_unaligned;
     constexpr int TP = SWIZZLED ? D : PITCH;               // elements between rows of a key or value tile
-    bf16* q_tile = reinterpret_cast<bf16*>(raw) + (SWIZZLED ? 4 * TILE * TP : 0);   // [8][PITCH]
+    bf16* q_tile = reinterpret_cast<bf16*>(raw) + (SWIZZLED ? BUFFERS * TILE * TP : 0);   // [8][PITCH]
     bf16* k_tiles = SWIZZLED ? reinterpret_cast<bf16*>(raw) : q_tile + 8 * PITCH;   // [2][64][TP]
     bf16* v_tiles = k_tiles + 2 * TILE * TP;                                        // [2][64][TP]
     // Where the eight elements from column `col` (a multiple of 8) of row `r` of a tile lie.
@@ -655,11 +660,12 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
         tile_first = tile_low + split * per_split;
         tiles = max(0, min(per_split, tile_high + 1 - tile_first));
     }
-    __shared__ unsigned long long tile_bar[2];
+    __shared__ unsigned long long tile_bar[3];
     if (tiles > 0) {
         if (threadIdx.x == 0) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&tile_bar[0])));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&tile_bar[1])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&tile_bar[2])));
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
         __syncthreads();
@@ -693,8 +699,31 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
                            slot, kv_head, tile, rows_to_copy(tile), &tile_bar[buffer]);
             }
         };
-        issue(tile_first, 0);
-        if (tiles > 1) issue(tile_first + 1, 1);
+        // The ring: three buffers that take, in turn, the keys of the block's tile 0, its values,
+        // the keys of tile 1, ... (load 2i: keys of tile i, load 2i + 1: its values), each on the
+        // barrier of its buffer. Two loads are on their way while a third is read; a block
+        // holds 3 instead of 4 tiles, so that four blocks of head width 128 fit an SM.
+        auto issue_load = [&](int load) {
+            if (threadIdx.x == 0) {
+                const int buffer = load % 3;
+                const int page_row = (int)(cache_row_offset(a.cache, slot, (tile_first + (load >> 1)) * TILE, kv_head) / D);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                                 smem_address(&tile_bar[buffer])),
+                             "r"((unsigned)(TILE * D * 2))
+                             : "memory");
+                for (int span = 0; span < D / 64; ++span)
+                    tensor_copy_2d(k_tiles + buffer * TILE * TP + span * TILE * 64, (load & 1) ? &v_map : &k_map,
+                                   &tile_bar[buffer], span * 64, page_row);
+            }
+        };
+        if (RING) {
+            issue_load(0);
+            issue_load(1);
+            if (tiles > 1) issue_load(2);
+        } else {
+            issue(tile_first, 0);
+            if (tiles > 1) issue(tile_first + 1, 1);
+        }
         uint4 new_raw = make_uint4(0u, 0u, 0u, 0u);          // warp 0: the new key row's chunk, warp 1: the value's
         if (has_new && warp < 2 && lane < CHUNKS)
             new_raw = *reinterpret_cast<const uint4*>((warp == 0 ? a.k_step : a.v_step) + (long long)row * a.ldkv +
@@ -722,7 +751,14 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
         unsigned q_frag[D / 16][2];                         // Q^T as B operand: (dims, head g)
         for (int index = 0; index < tiles; ++index) {
             const int tile = tile_first + index, buffer = index & 1;
-            wait_tile(&tile_bar[buffer], (index >> 1) & 1);
+            const int k_load = 2 * index, v_load = 2 * index + 1;                 // the ring's loads of this tile
+            const bool newest = has_new && tile == new_tile;
+            if (RING) {
+                wait_tile(&tile_bar[k_load % 3], (k_load / 3) & 1);
+                if (newest) wait_tile(&tile_bar[v_load % 3], (v_load / 3) & 1);   // the step's value goes into the value tile
+            } else {
+                wait_tile(&tile_bar[buffer], (index >> 1) & 1);
+            }
             if (index == 0) {
                 copy_async_wait<0>();
                 // The rows zeroed above will be overwritten by later copies: order the two kinds of write.
@@ -760,9 +796,9 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
                 }
             }
             const int first_key = warp * 16;
-            bf16* k_tile = k_tiles + buffer * TILE * TP;
-            bf16* v_tile = v_tiles + buffer * TILE * TP;
-            if (has_new && tile == new_tile) {              // the step's own key (warp 0) and value (warp 1)
+            bf16* k_tile = k_tiles + (RING ? k_load % 3 : buffer) * TILE * TP;
+            bf16* v_tile = RING ? k_tiles + (v_load % 3) * TILE * TP : v_tiles + buffer * TILE * TP;
+            if (newest) {                                   // the step's own key (warp 0) and value (warp 1)
                 const int r_new = position - tile * TILE;
                 if (warp < 2) {
                     uint4 fresh = new_raw;
@@ -789,7 +825,9 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
                 }
                 __syncthreads();
             }
-            if (tile * TILE + first_key <= position && tile * TILE + first_key + 15 >= low) {
+            const bool active = tile * TILE + first_key <= position && tile * TILE + first_key + 15 >= low;
+            unsigned p0 = 0u, p1 = 0u;
+            if (active) {
                 float s[4] = {0.f, 0.f, 0.f, 0.f};          // keys g (0,1) and g+8 (2,3) x heads 2t, 2t+1
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -828,8 +866,15 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
                 for (int n = 0; n < D / 16; ++n) {
                     o[n][0] *= keep[0]; o[n][1] *= keep[1]; o[n][2] *= keep[0]; o[n][3] *= keep[1];
                 }
-                const unsigned p0 = transpose_8x8(pack_bf16(s[0], s[1]));   // keys 2t, 2t+1 of head g
-                const unsigned p1 = transpose_8x8(pack_bf16(s[2], s[3]));   // keys 2t+8, 2t+9
+                p0 = transpose_8x8(pack_bf16(s[0], s[1]));   // keys 2t, 2t+1 of head g
+                p1 = transpose_8x8(pack_bf16(s[2], s[3]));   // keys 2t+8, 2t+9
+            }
+            if (RING) {
+                __syncthreads();                            // the keys are read: their buffer takes the next values
+                if (v_load + 2 < 2 * tiles) issue_load(v_load + 2);
+                wait_tile(&tile_bar[v_load % 3], (v_load / 3) & 1);
+            }
+            if (active) {
 #pragma unroll
                 for (int n = 0; n < D / 16; ++n) {          // V^T as A operand: 16 dims x 16 keys
                     unsigned v_frag[4];
@@ -838,7 +883,11 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
                 }
             }
             __syncthreads();
-            if (index + 2 < tiles) issue(tile + 2, buffer);  // the buffer that was just read takes the tile after next
+            if (RING) {
+                if (k_load + 4 < 2 * tiles) issue_load(k_load + 4);   // the values are read: the keys of the tile after next
+            } else if (index + 2 < tiles) {
+                issue(tile + 2, buffer);                     // the buffer that was just read takes the tile after next
+            }
         }
     }
 #pragma unroll
@@ -853,7 +902,7 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
     float* merge_stat = merge_out + 4 * 8 * D;                           // [4][8][2]
     // What the other blocks of a cluster send (never used for anything else: a block that is
     // ahead may send while this one still works on its tiles).
-    float* recv_out = reinterpret_cast<float*>(raw + (SWIZZLED ? SWIZZLED_TILE_BYTES : NARROW_TILE_BYTES));   // [splits][share]
+    float* recv_out = reinterpret_cast<float*>(raw + (RING ? RING_TILE_BYTES : SWIZZLED ? SWIZZLED_TILE_BYTES : NARROW_TILE_BYTES));   // [splits][share]
     float* recv_stat = recv_out + NARROW_RECV_OUT_FLOATS;                // [8 splits][8 heads][2]
     cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
     __syncthreads();
@@ -1026,6 +1075,7 @@ __global__ void attention_combine_kernel(Args a) {
 
 constexpr size_t PREFILL_SHARED = (size_t)(TILE + 4 * TILE) * PITCH * sizeof(bf16);
 int kidi_decode_swizzled = 1;
+int kidi_decode_ring = 1;
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1065,6 +1115,19 @@ KIDI_API int kidi_attention_head_dim() { return D; }
 
 // 0: the decode kernel copies pages row by row into padded tiles whatever the head width.
 KIDI_API void kidi_attention_decode_swizzled(int enabled) { kidi_decode_swizzled = enabled; }
+
+// 0: the page-copying decode kernel keeps two key and two value tiles (three blocks of head
+// width 128 an SM) instead of a ring of three tiles (four blocks).
+KIDI_API void kidi_attention_decode_ring(int enabled) { kidi_decode_ring = enabled; }
+
+// Decode blocks of the kernel for up to eight query heads a key/value head that fit an SM
+// by shared memory (`swizzled`: the cache is one contiguous array and pages are copied whole).
+KIDI_API int kidi_attention_decode_blocks_per_sm(int swizzled) {
+    const size_t block = (swizzled && kidi_decode_swizzled && D % 64 == 0)
+                             ? (kidi_decode_ring ? RING_SHARED : SWIZZLED_SHARED) : NARROW_SHARED;
+    const int fitting = (int)((228 * 1024) / (block + 1024));       // a kilobyte a block is the system's
+    return fitting < 1 ? 1 : fitting > 4 ? 4 : fitting;             // four by registers
+}
 
 // Whether a bounded wait for a tile ever ran out in this process (reads the flag back; synchronises).
 KIDI_API int kidi_attention_timeout_flag() {
@@ -1124,31 +1187,40 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   (int)DECODE_SHARED);
-        const void* narrow[4] = {(const void*)attention_decode_narrow_kernel<false, false>,
-                                 (const void*)attention_decode_narrow_kernel<true, false>,
-                                 (const void*)attention_decode_narrow_kernel<false, true>,
-                                 (const void*)attention_decode_narrow_kernel<true, true>};
-        for (int i = 0; i < 4 && status == cudaSuccess; ++i)
-            status = cudaFuncSetAttribute(narrow[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)(i >= 2 ? SWIZZLED_SHARED : NARROW_SHARED));
+        const void* narrow[6] = {(const void*)attention_decode_narrow_kernel<false, 0>,
+                                 (const void*)attention_decode_narrow_kernel<true, 0>,
+                                 (const void*)attention_decode_narrow_kernel<false, 1>,
+                                 (const void*)attention_decode_narrow_kernel<true, 1>,
+                                 (const void*)attention_decode_narrow_kernel<false, 2>,
+                                 (const void*)attention_decode_narrow_kernel<true, 2>};
+        const size_t sizes[3] = {NARROW_SHARED, SWIZZLED_SHARED, RING_SHARED};
+        for (int i = 0; i < 6 && status == cudaSuccess; ++i)
+            status = cudaFuncSetAttribute(narrow[i], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizes[i >> 1]);
         if (status != cudaSuccess) return (int)status;
         configured = true;
     }
     dim3 grid(a.splits, a.kv_heads, a.rows);
-    const size_t narrow_shared = swizzled ? SWIZZLED_SHARED : NARROW_SHARED;
-    if (clustered)
-        return swizzled ? kidi_launch_clusters(attention_decode_narrow_kernel<true, true>, grid, THREADS, narrow_shared,
-                                               stream, (unsigned)a.splits, k_map, v_map, a)
-                        : kidi_launch_clusters(attention_decode_narrow_kernel<true, false>, grid, THREADS, narrow_shared,
-                                               stream, (unsigned)a.splits, k_map, v_map, a);
+    const int form = !swizzled ? 0 : kidi_decode_ring ? 2 : 1;
+    const size_t narrow_shared = form == 2 ? RING_SHARED : form == 1 ? SWIZZLED_SHARED : NARROW_SHARED;
+    if (clustered) {
+        const unsigned cluster = (unsigned)a.splits;
+        if (form == 2)
+            return kidi_launch_clusters(attention_decode_narrow_kernel<true, 2>, grid, THREADS, narrow_shared, stream,
+                                        cluster, k_map, v_map, a);
+        if (form == 1)
+            return kidi_launch_clusters(attention_decode_narrow_kernel<true, 1>, grid, THREADS, narrow_shared, stream,
+                                        cluster, k_map, v_map, a);
+        return kidi_launch_clusters(attention_decode_narrow_kernel<true, 0>, grid, THREADS, narrow_shared, stream, cluster,
+                                    k_map, v_map, a);
+    }
     int status;
     if (group > 8) status = kidi_launch(attention_decode_kernel, grid, THREADS, DECODE_SHARED, stream, a);
-    else if (swizzled)
-        status = kidi_launch(attention_decode_narrow_kernel<false, true>, grid, THREADS, narrow_shared, stream, k_map,
-                             v_map, a);
+    else if (form == 2)
+        status = kidi_launch(attention_decode_narrow_kernel<false, 2>, grid, THREADS, narrow_shared, stream, k_map, v_map, a);
+    else if (form == 1)
+        status = kidi_launch(attention_decode_narrow_kernel<false, 1>, grid, THREADS, narrow_shared, stream, k_map, v_map, a);
     else
-        status = kidi_launch(attention_decode_narrow_kernel<false, false>, grid, THREADS, narrow_shared, stream, k_map,
-                             v_map, a);
+        status = kidi_launch(attention_decode_narrow_kernel<false, 0>, grid, THREADS, narrow_shared, stream, k_map, v_map, a);
     if (status || a.splits == 1 || (group <= 8 && a.counters)) return status;
     dim3 combine(a.heads, a.rows);
     return kidi_launch(attention_combine_kernel, combine, D >= 128 ? 128 : 64, 0, stream, a);

@@ -27,6 +27,9 @@ FUSE_ROTATION = os.environ.get("KIDI_B200_FUSE_ROTATION", "1") == "1"
 # Head widths that are multiples of 64: the decode kernel takes whole pages by TMA tensor copies
 # (0: row by row into padded tiles, as for the other widths).
 DECODE_SWIZZLED = os.environ.get("KIDI_B200_DECODE_SWIZZLED", "1") == "1"
+# The page-copying decode kernel keeps a ring of three tiles (keys and values in turn), so that
+# four blocks of head width 128 fit an SM (0: two key and two value tiles, three blocks).
+DECODE_RING = os.environ.get("KIDI_B200_DECODE_RING", "1") == "1"
 # Up to this many splits merge inside a thread-block cluster (no workspace, no second kernel);
 # 0 switches that off.
 CLUSTER_SPLITS = int(os.environ.get("KIDI_B200_CLUSTER_SPLITS", "8"))
@@ -49,6 +52,7 @@ class FastAttentionArgs(ctypes.Structure):
 _libraries: Dict[int, ctypes.CDLL] = {}
 _tensor_memory_libraries: Dict[int, ctypes.CDLL] = {}
 _sm_count: Dict[int, int] = {}
+_ring_set: Dict[int, bool] = {}      # the decode form each library was last switched to
 
 
 def library(head_dim: int) -> ctypes.CDLL:
@@ -62,6 +66,10 @@ def library(head_dim: int) -> ctypes.CDLL:
         lib.kidi_attention_decode_swizzled.argtypes = [c_int]
         lib.kidi_attention_decode_swizzled.restype = None
         lib.kidi_attention_decode_swizzled(1 if DECODE_SWIZZLED else 0)
+        lib.kidi_attention_decode_ring.argtypes = [c_int]
+        lib.kidi_attention_decode_ring.restype = None
+        lib.kidi_attention_decode_ring(0)
+        _ring_set[head_dim] = False
         ops.configure_library(lib)
         _libraries[head_dim] = lib
     return lib
@@ -141,12 +149,34 @@ def sm_count(device: torch.device) -> int:
     return _sm_count[index]
 
 
-def blocks_per_sm(head_dim: int = 128) -> int:
-    """Decode attention blocks that fit one SM: 8 query rows and four 64-row tiles with rows
-    padded by 8 elements, plus what a cluster's blocks send each other; at most four by
-    registers. Three at head width 128."""
-    block = (8 + 4 * 64) * (head_dim + 8) * 2 + (8 * head_dim + 8 + 128) * 4 + 1024
+def ring_available(head_dim: int) -> bool:
+    return DECODE_SWIZZLED and DECODE_RING and head_dim % 64 == 0
+
+
+def blocks_per_sm(head_dim: int = 128, ring: bool = False) -> int:
+    """Decode attention blocks that fit one SM: 8 query rows, the tiles (four 64-row tiles with
+    rows padded by 8 elements, or with `ring` three unpadded ones), what a cluster's blocks send
+    each other and a kilobyte of the system's; at most four by registers. Three at head width
+    128, four with the ring."""
+    received = (8 * head_dim + 8 + 128) * 4
+    if ring:
+        block = 1024 + (3 * 64 * head_dim + 8 * (head_dim + 8)) * 2 + received + 1024
+    else:
+        block = (8 + 4 * 64) * (head_dim + 8) * 2 + received + 1024
     return max(1, min(4, (228 * 1024) // block))
+
+
+def decode_ring(rows: int, kv_heads: int, device: torch.device, head_dim: int) -> bool:
+    """Whether decode attention takes its ring form: one block per (row, key/value head), no
+    splits. The ring holds fewer bytes in flight per block and pays a second barrier per
+    tile (measured on a B200 at head width 128: 8.4 against 7.8 us a layer at batch 1, 28.6
+    against 26.1 at batch 32), so it is taken only where a fourth block per SM saves a round
+    of blocks: 46.6 against 53.5 us a layer at batch 64 and 1,060 tokens."""
+    if not ring_available(head_dim):
+        return False
+    items, sms = max(1, rows * kv_heads), sm_count(device)
+    with_ring, without = blocks_per_sm(head_dim, True) * sms, blocks_per_sm(head_dim, False) * sms
+    return -(-items // with_ring) < -(-items // without)
 
 
 # What a block spends beside its tiles (launch, tables, query, merge of the splits), in tile
@@ -164,6 +194,8 @@ def decode_splits(rows: int, kv_heads: int, longest: int, device: torch.device, 
     forced = int(os.environ.get("KIDI_B200_DECODE_SPLITS", "0"))
     if forced:
         return max(1, min(pages, forced))
+    if decode_ring(rows, kv_heads, device, head_dim):
+        return 1
     slots = blocks_per_sm(head_dim) * sm_count(device)
     items = max(1, rows * kv_heads)
     best, best_cost = 1, None
@@ -242,7 +274,14 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
         # against 17.1 us a layer at batch 8). Clusters that must wait for several free slots of
         # one GPC at once lose that again when the grid takes more than a wave (70.6 against
         # 67.0 us at batch 64).
-        one_wave = qkv.shape[0] * kv_heads * splits <= blocks_per_sm(head_dim) * sm_count(qkv.device)
+        ring = getattr(ctx, "decode_ring", None)           # a test may ask for either form
+        if ring is None:
+            ring = splits == 1 and decode_ring(qkv.shape[0], kv_heads, qkv.device, head_dim)
+        ring = bool(ring) and ring_available(head_dim)
+        if _ring_set.get(head_dim) != ring:                # the form is a switch of the library, not of a launch
+            lib.kidi_attention_decode_ring(1 if ring else 0)
+            _ring_set[head_dim] = ring
+        one_wave = qkv.shape[0] * kv_heads * splits <= blocks_per_sm(head_dim, ring) * sm_count(qkv.device)
         clustered = 1 < splits <= CLUSTER_SPLITS and heads // kv_heads <= 8 and one_wave
         if splits > 1 and not clustered:
             workspace = ctx.workspace("attention_partial", qkv.shape[0] * heads * splits * (head_dim + 2))

@@ -264,9 +264,10 @@ def reference_attention(q, keys, values, positions, window, scale):
 class FakeContext:
     """What the attention launcher needs of a step."""
 
-    def __init__(self, plan, tables, splits=None):
+    def __init__(self, plan, tables, splits=None, ring=None):
         self.plan, self.tables = plan, tables
         self.decode_splits = splits
+        self.decode_ring = ring           # None: the launcher's own choice of the decode kernel's form
         self._held = {}
 
     def workspace(self, name, count, zero=False):
@@ -275,14 +276,14 @@ class FakeContext:
         return self._held[name]
 
 
-def launch_attention(kind, plan, tables, qkv, out, splits=None, **arguments):
+def launch_attention(kind, plan, tables, qkv, out, splits=None, ring=None, **arguments):
     from kidi_b200.kernels import attention, ops
     if kind == "generic":
         ops.attention_generic(qkv, out, tables=tables, **arguments)
     else:
         assert attention.fast_fits(qkv.dtype, arguments["heads"], arguments["kv_heads"], arguments["head_dim"],
                                    plan.is_decode and not arguments["keys_in_step"])
-        attention.run(FakeContext(plan, tables, splits), qkv, out, **arguments)
+        attention.run(FakeContext(plan, tables, splits, ring), qkv, out, **arguments)
 
 
 @pytest.mark.parametrize("kind,dtype", [("generic", torch.float32), ("generic", torch.bfloat16),
@@ -413,6 +414,21 @@ def test_attention_decode(kind, dtype, geometry, splits):
         q = qkv[index:index + 1, :heads * head_dim].float().reshape(1, heads, head_dim)
         expected = reference_attention(q, keys, values, [start], window, scale)
         close(out[index:index + 1], expected, tolerance, f"{kind}: sequence of {start + 1} tokens, {splits} splits")
+    if kind == "tensor_core" and head_dim % 64 == 0:
+        # The ring form of the page-copying kernel (three tiles that take keys and values in
+        # turn), which the launcher takes by itself only for large batches.
+        from kidi_b200.kernels import attention
+        assert attention.ring_available(head_dim)
+        ring_out = torch.empty_like(out)
+        launch_attention(kind, plan, tables, qkv.to(DEVICE), ring_out, splits=splits, ring=True, heads=heads,
+                         kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window, kv_view=view,
+                         keys_in_step=False)
+        for index, start in enumerate(starts):
+            keys, values = history[index]
+            q = qkv[index:index + 1, :heads * head_dim].float().reshape(1, heads, head_dim)
+            expected = reference_attention(q, keys, values, [start], window, scale)
+            close(ring_out[index:index + 1], expected, tolerance, f"ring: sequence of {start + 1} tokens, {splits} splits")
+        assert attention.timeout_flags() == 0
     if kind == "tensor_core" and splits == 3:
         # Three splits merge inside a thread-block cluster; the same splits merged through a
         # workspace in global memory must agree.
@@ -505,7 +521,8 @@ def test_decode_with_the_rotation_inside(geometry, splits, norm_dtype):
     else:
         cos = sin = None
     results = []
-    for fused in (False, True):
+    forms = [(False, None), (True, None)] + ([(True, True)] if attention.ring_available(head_dim) else [])
+    for fused, ring in forms:
         cache, slots, plan, tables = make_cache_and_tables(starts, news, kv_heads, head_dim, window, torch.bfloat16,
                                                            max_tokens=8192)
         view = cache.views(0)[0]
@@ -523,16 +540,17 @@ def test_decode_with_the_rotation_inside(geometry, splits, norm_dtype):
             ops.rope_store(rows, q_norm=q_norm, k_norm=k_norm, eps=1e-6, cos=cos, sin=sin, rotary_dim=rotary_dim,
                            tables=tables, kv_view=view, store=True, **common)
             rotation = None
-        attention.run(FakeContext(plan, tables, splits), rows, out, scale=scale, window=window, kv_view=view,
+        attention.run(FakeContext(plan, tables, splits, ring), rows, out, scale=scale, window=window, kv_view=view,
                       keys_in_step=False, rotation=rotation, **common)
         torch.cuda.synchronize()
         results.append((out, view.keys.clone(), view.values.clone(), [view.group.pages[slot] for slot in slots]))
-    (plain_out, plain_keys, plain_values, plain_pages), (fused_out, fused_keys, fused_values, fused_pages) = results
-    assert plain_pages == fused_pages
-    assert torch.equal(fused_keys, plain_keys), "the keys written by the attention kernel differ from the separate kernel's"
-    assert torch.equal(fused_values, plain_values)
-    assert torch.isfinite(fused_out.float()).all()
-    close(fused_out, plain_out, 8e-3, "attention with the rotation inside")      # one bfloat16 step
+    plain_out, plain_keys, plain_values, plain_pages = results[0]
+    for fused_out, fused_keys, fused_values, fused_pages in results[1:]:       # the usual form, then the ring
+        assert plain_pages == fused_pages
+        assert torch.equal(fused_keys, plain_keys), "the keys written by the attention kernel differ from the separate kernel's"
+        assert torch.equal(fused_values, plain_values)
+        assert torch.isfinite(fused_out.float()).all()
+        close(fused_out, plain_out, 8e-3, "attention with the rotation inside")      # one bfloat16 step
     assert attention.timeout_flags() == 0
 
 
