@@ -49,7 +49,7 @@ class GatedFeedForward(Part):
         from ..kernels import skinny, tcgen05
         if skinny.fits(x, self.gate_up.weight):
             gated = skinny.gemm_silu_gate(x, self.gate_up.weight)
-        elif x.shape[0] >= tcgen05.MIN_GATED_ROWS and tcgen05.fits(x, self.gate_up.weight):
+        elif tcgen05.MIN_GATED_ROWS <= x.shape[0] <= tcgen05.MAX_GATED_ROWS and tcgen05.fits(x, self.gate_up.weight):
             gated = tcgen05.gemm_silu_gate(x, self.gate_up.weight)
         else:
             gated = ops.silu_gate(self.gate_up.forward(x))
