@@ -8,10 +8,11 @@ registered part. Which kernel runs follows the element types:
   multiply-adds; no reduced-precision matrix mode);
 * bfloat16 by bfloat16 with up to 8 rows (decode): the weight-streaming `mma.sync`
   kernel of this package (`kernels/skinny.py`);
-* bfloat16 by bfloat16 with 9 to 64 rows and a large weight (16384 output features or
+* bfloat16 by bfloat16 with 9 to 16 rows and a large weight (16384 output features or
   more: the fused gate/up projection, the output head): this package's tcgen05 kernel
   (`kernels/tcgen05.py`: TMA-fed, accumulating in tensor memory), which streams such
-  weights as fast as the vendor library does;
+  weights as fast as the vendor library does up to there (and takes up to 64 rows when
+  KIDI_B200_TCGEN05_MAX_ROWS says so);
 * bfloat16 by bfloat16 otherwise: the vendor matrix library through `torch.mm`, which
   is where the reference's CUDA engine calls a library too
   (docs/cuda-performance-plan.md:47-52).
