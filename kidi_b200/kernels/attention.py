@@ -29,7 +29,9 @@ FUSE_ROTATION = os.environ.get("KIDI_B200_FUSE_ROTATION", "1") == "1"
 DECODE_SWIZZLED = os.environ.get("KIDI_B200_DECODE_SWIZZLED", "1") == "1"
 # The page-copying decode kernel keeps a ring of three tiles (keys and values in turn), so that
 # four blocks of head width 128 fit an SM (0: two key and two value tiles, three blocks).
-DECODE_RING = os.environ.get("KIDI_B200_DECODE_RING", "1") == "1"
+# "force": wherever the kernel has that form (for tests of it on small batches).
+DECODE_RING = os.environ.get("KIDI_B200_DECODE_RING", "1") in ("1", "force")
+DECODE_RING_ALWAYS = os.environ.get("KIDI_B200_DECODE_RING", "1") == "force"
 # Up to this many splits merge inside a thread-block cluster (no workspace, no second kernel);
 # 0 switches that off.
 CLUSTER_SPLITS = int(os.environ.get("KIDI_B200_CLUSTER_SPLITS", "8"))
@@ -174,6 +176,8 @@ def decode_ring(rows: int, kv_heads: int, device: torch.device, head_dim: int) -
     of blocks: 46.6 against 53.5 us a layer at batch 64 and 1,060 tokens."""
     if not ring_available(head_dim):
         return False
+    if DECODE_RING_ALWAYS:
+        return True
     items, sms = max(1, rows * kv_heads), sm_count(device)
     with_ring, without = blocks_per_sm(head_dim, True) * sms, blocks_per_sm(head_dim, False) * sms
     return -(-items // with_ring) < -(-items // without)
