@@ -107,15 +107,16 @@ __device__ __forceinline__ void prefetch_l2(const void* pointer) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(pointer));
 }
 
-extern int kidi_pdl_flag;  // one per library; 0 launches every kernel the ordinary way
+extern int kidi_pdl_flag;  // one per library; 0 launches every kernel the ordinary way, bit 0 every
+                           // kernel as a dependent launch, bit 1 only the small ones (kidi_launch_small)
 
 #define KIDI_DEFINE_PDL_FLAG()                                              \
     int kidi_pdl_flag = 0;                                                  \
     KIDI_API void kidi_set_pdl(int enabled) { kidi_pdl_flag = enabled; }
 
 template <typename... Expected, typename... Actual>
-static inline int kidi_launch(void (*kernel)(Expected...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
-                              Actual&&... arguments) {
+static inline int kidi_launch_as(bool dependent, void (*kernel)(Expected...), dim3 grid, dim3 block, size_t shared,
+                                 cudaStream_t stream, Actual&&... arguments) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
@@ -125,9 +126,23 @@ static inline int kidi_launch(void (*kernel)(Expected...), dim3 grid, dim3 block
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = kidi_pdl_flag ? 1 : 0;
+    config.numAttrs = dependent ? 1 : 0;
     cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<Expected>(arguments)...);
     return status != cudaSuccess ? (int)status : (int)cudaGetLastError();
+}
+
+template <typename... Expected, typename... Actual>
+static inline int kidi_launch(void (*kernel)(Expected...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
+                              Actual&&... arguments) {
+    return kidi_launch_as((kidi_pdl_flag & 1) != 0, kernel, grid, block, shared, stream, static_cast<Actual&&>(arguments)...);
+}
+
+// A kernel of a few small blocks between two large ones (a norm between two products): as a
+// dependent launch its blocks are resident, waiting, when the kernel before it ends.
+template <typename... Expected, typename... Actual>
+static inline int kidi_launch_small(void (*kernel)(Expected...), dim3 grid, dim3 block, size_t shared,
+                                    cudaStream_t stream, Actual&&... arguments) {
+    return kidi_launch_as((kidi_pdl_flag & 3) != 0, kernel, grid, block, shared, stream, static_cast<Actual&&>(arguments)...);
 }
 
 // The same with the blocks along x grouped into thread-block clusters of `cluster_x`
@@ -148,7 +163,7 @@ static inline int kidi_launch_clusters(void (*kernel)(Expected...), dim3 grid, d
     attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = kidi_pdl_flag ? 2 : 1;
+    config.numAttrs = (kidi_pdl_flag & 1) ? 2 : 1;
     cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<Expected>(arguments)...);
     return status != cudaSuccess ? (int)status : (int)cudaGetLastError();
 }

@@ -148,7 +148,7 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const void* we
                          !((uintptr_t)y & 15);
 #define KIDI_VECTOR_CASE(CHUNKS)                                                                              \
     if (vectors && hidden == THREADS * 4 * CHUNKS)                                                            \
-        return kidi_launch(add_rmsnorm_vector_kernel<TD, TW, TY, THREADS, CHUNKS>, rows, THREADS, 0, stream,   \
+        return kidi_launch_small(add_rmsnorm_vector_kernel<TD, TW, TY, THREADS, CHUNKS>, rows, THREADS, 0, stream, \
                            residual, (const TD*)delta, (const TW*)weight, (TY*)y, row_index, eps, write_residual);
     KIDI_VECTOR_CASE(1)
     KIDI_VECTOR_CASE(2)
@@ -162,7 +162,7 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const void* we
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (status != cudaSuccess) return (int)status;
     }
-    return kidi_launch(kernel, rows, THREADS, shared, stream, residual, (const TD*)delta, (const TW*)weight, (TY*)y,
+    return kidi_launch_small(kernel, rows, THREADS, shared, stream, residual, (const TD*)delta, (const TW*)weight, (TY*)y,
                        row_index, hidden, eps, write_residual);
 }
 

@@ -92,12 +92,13 @@ def core():
 
 
 def configure_library(lib) -> None:
-    """Settings every kernel library takes: KIDI_B200_PDL=1 launches kernels with
-    programmatic dependent launch (an experiment switch; off by default)."""
+    """Settings every kernel library takes: KIDI_B200_PDL=1 launches every kernel with
+    programmatic dependent launch, KIDI_B200_PDL=norm only the norms between the products
+    (experiment switches; off by default)."""
     import os
     lib.kidi_set_pdl.argtypes = [c_int]
     lib.kidi_set_pdl.restype = None
-    lib.kidi_set_pdl(1 if os.environ.get("KIDI_B200_PDL", "0") == "1" else 0)
+    lib.kidi_set_pdl({"1": 1, "norm": 2}.get(os.environ.get("KIDI_B200_PDL", "0"), 0))
 
 
 # ----------------------------------------------------------------- structures
