@@ -2,7 +2,7 @@
 
     kidi_b200 generate -m MODEL [-i FILE] [-o FILE] [--max-new-tokens N] [--context-size N]
                        [--prefill-chunk-size N] [--ignore-eos] [--cache-tokens N] [--max-active N]
-                       [--precision checkpoint|bf16|fp32] [--backend auto|cuda[:INDEX]] [--profile]
+                       [--precision checkpoint|bf16|fp32] [--cast-weights] [--backend auto|cuda[:INDEX]] [--profile]
                        [--temperature T] [--seed S]
     kidi_b200 inspect -m MODEL
     kidi_b200 random-model --config CONFIG.json --seed S -o MODEL [--precision bf16|fp32]
@@ -64,6 +64,8 @@ def build_parser() -> argparse.ArgumentParser:
     generate.add_argument("--ignore-eos", dest="ignore_eos", action="store_true")
     generate.add_argument("--precision", default="checkpoint", choices=["checkpoint", "bf16", "fp32"],
                           help="compute policy; checkpoint follows the dtype of the weights file")
+    generate.add_argument("--cast-weights", dest="cast_weights", action="store_true",
+                          help="round matrices stored wider than bfloat16 to bfloat16 (implied by --precision bf16)")
     generate.add_argument("--kv-cache-precision", dest="kv_cache_precision", default="auto",
                           choices=["auto", "fp32", "bf16"], help="auto: the compute precision")
     generate.add_argument("--max-active", dest="max_active", type=int, default=None, metavar="N",
@@ -143,7 +145,10 @@ def _generate(args) -> int:
     if args.cache_tokens <= 0 or args.queue_size <= 0:
         raise invalid_argument("--cache-tokens and --queue-size must be positive")
     max_active = args.max_active if args.max_active is not None else DEFAULT_MAX_ACTIVE
-    engine = Engine.load(args.model, dtype=precision, device=device, max_tokens=args.cache_tokens)
+    # An explicit --precision bf16 asks for bfloat16 products: matrices a file stores wider are
+    # rounded at load. With "checkpoint" every tensor keeps the width the file stores it in.
+    engine = Engine.load(args.model, dtype=precision, device=device, max_tokens=args.cache_tokens,
+                         cast_weights=args.precision == "bf16" or args.cast_weights)
     load_ns = time.perf_counter_ns() - started
 
     source = sys.stdin if args.input == "-" else open(args.input, "r", encoding="utf-8")

@@ -90,8 +90,10 @@ class Engine:
     # ---------------------------------------------------------------- loading
     @classmethod
     def load(cls, model_dir: str, *, dtype="bfloat16", device="cuda:0", max_tokens: int = 4096,
-             max_slots: Optional[int] = None) -> "Engine":
-        """From a folder with config.json and model.safetensors; config.json chooses the model."""
+             max_slots: Optional[int] = None, cast_weights: bool = False) -> "Engine":
+        """From a folder with config.json and model.safetensors (or the shards its index
+        names); config.json chooses the model. A tensor keeps the width the file stores it
+        in; with `cast_weights` a bfloat16 engine rounds wider matrices to bfloat16."""
         engine_dtype = _dtype(dtype)
         _require_cuda(device)
         _, typed, spec = spec_from_config(read_config_json(model_dir))
@@ -100,7 +102,8 @@ class Engine:
         try:
             with torch.cuda.device(model.env.device):
                 model.bind(bind_parameters(model.parameters(), checkpoint, engine_dtype=engine_dtype,
-                                           device=model.env.device, ignored=spec.ignored_tensors))
+                                           device=model.env.device, ignored=model.ignored_tensors(),
+                                           cast_matrices=cast_weights))
         finally:
             checkpoint.close()
         return cls(model, max_tokens=max_tokens, max_slots=max_slots, config=typed)
@@ -108,7 +111,7 @@ class Engine:
     @classmethod
     def from_config(cls, config: Mapping[str, Any], *, seed: int = 0, dtype="bfloat16", device="cuda:0",
                     max_tokens: int = 4096, max_slots: Optional[int] = None,
-                    tensors: Optional[Mapping[str, torch.Tensor]] = None) -> "Engine":
+                    tensors: Optional[Mapping[str, torch.Tensor]] = None, cast_weights: bool = False) -> "Engine":
         """From a config.json dictionary, with random weights drawn on the device from
         `seed`, or with the checkpoint tensors given in `tensors`."""
         engine_dtype = _dtype(dtype)
@@ -118,7 +121,8 @@ class Engine:
         with torch.cuda.device(model.env.device):
             if tensors is not None:
                 bound = bind_parameters(model.parameters(), TensorDict(tensors), engine_dtype=engine_dtype,
-                                        device=model.env.device, ignored=spec.ignored_tensors)
+                                        device=model.env.device, ignored=model.ignored_tensors(),
+                                        cast_matrices=cast_weights)
             else:
                 bound = random_parameters(model.parameters(), seed, engine_dtype, model.env.device)
             model.bind(bound)

@@ -67,6 +67,22 @@ class CausalLM:
             raise invalid_argument("two parts declare the same tensor name")
         return found
 
+    def ignored_tensors(self) -> List[str]:
+        """Regular expressions of tensor names a checkpoint may carry unused: the model's
+        own and those its parts name relative to their prefixes."""
+        import re
+
+        def collect(part: Part) -> List[str]:
+            found = ["^" + re.escape(part.prefix) + pattern.lstrip("^") for pattern in part.ignored_tensors()]
+            for child in part.children():
+                found.extend(collect(child))
+            return found
+
+        patterns = list(self.spec.ignored_tensors)
+        for part in self._top_parts():
+            patterns.extend(collect(part))
+        return patterns
+
     def bind(self, bound: Dict[str, torch.Tensor]) -> None:
         for part in self._top_parts():
             bind_all(part, bound)

@@ -44,12 +44,39 @@ def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
 
 
 launch_count = 0  # kernels of this package launched (or captured into a graph) so far
+_launch_log: Optional[list] = None
+
+
+class record_launches:
+    """Collects, while it is open, the name of every kernel this package launches and of every
+    product handed to the vendor library (`library_mm`), in order: `with record_launches() as
+    names: ...`. Names carry the form a launcher chose, e.g. `attention_decode[ring]`, so that a
+    test can assert which branch of a dispatch ran."""
+
+    def __enter__(self) -> list:
+        global _launch_log
+        self._outer, _launch_log = _launch_log, []
+        return _launch_log
+
+    def __exit__(self, *exc) -> None:
+        global _launch_log
+        inner, _launch_log = _launch_log, self._outer
+        if self._outer is not None:
+            self._outer.extend(inner)
+
+
+def note(what: str) -> None:
+    """Records work that is not one of this package's kernels (a vendor-library product)."""
+    if _launch_log is not None:
+        _launch_log.append(what)
 
 
 def _check(status: int, what: str, launches: int = 1) -> None:
     global launch_count
     if status == 0:
         launch_count += launches
+        if _launch_log is not None:
+            _launch_log.append(what)
         return
     if status == -2:
         raise unsupported(f"{what}: this combination of element types is not compiled")

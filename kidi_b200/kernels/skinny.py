@@ -86,5 +86,5 @@ def gemm_silu_gate(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Te
         out = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
     _check(_library().kidi_gemm_skinny(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), M, inter, K,
                                        x.stride(0), weight.stride(0), out.stride(0), 1, row_tiles, _stream()),
-           "gemm_silu_gate")
+           "gemm_silu_gate[skinny]")
     return out

@@ -106,7 +106,7 @@ def _run(x, weight, out, features: int, gated: bool, splits: Optional[int]) -> N
     _check(_library().kidi_gemm_tcgen05(
         _ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), rows, features, K, x.stride(0), weight.stride(0),
         out.stride(0), 1 if gated else 0, splits, _ptr(workspace), _ptr(counters), _ptr(error), _stream()),
-        "gemm_tcgen05")
+        "gemm_silu_gate[tcgen05]" if gated else "gemm_tcgen05")
 
 
 def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,

@@ -50,6 +50,12 @@ class Part:
         """The tensors this part owns, named relative to its prefix."""
         return []
 
+    def ignored_tensors(self) -> Sequence[str]:
+        """Regular expressions, relative to the part's prefix, of tensors a checkpoint may
+        carry for this part without the part using them (the reference's IGNORE mapping,
+        src/kidi/checkpoint/weights.h:20-24)."""
+        return ()
+
     def children(self) -> Sequence["Part"]:
         return ()
 

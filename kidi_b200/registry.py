@@ -56,8 +56,10 @@ def resolve_architecture(config: Mapping[str, Any]) -> Architecture:
         raise invalid_manifest("'architectures' must be a non-empty list of strings")
     if key is None or key not in _ARCHITECTURES:
         model_type = config.get("model_type")
-        if isinstance(model_type, str) and model_type in _ARCHITECTURES:
-            key = model_type
+        if model_type is not None and not isinstance(model_type, str):
+            raise invalid_manifest("'model_type' must be a string")
+        if isinstance(model_type, str) and (model_type in _ARCHITECTURES or key is None):
+            key = model_type        # a name nobody registered is reported as unsupported below
     if key is None:
         raise invalid_manifest("config.json names no architecture ('architectures' or 'model_type')")
     entry = _ARCHITECTURES.get(key)

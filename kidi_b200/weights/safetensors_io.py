@@ -6,7 +6,8 @@ u64 header length, a JSON header {name: {dtype, shape, data_offsets}} in which
 `__metadata__` is skipped, then the payload; limits of 8 dimensions, one million
 tensors and (here) a 100 MiB header; every entry must satisfy
 `end - begin == numel * itemsize`, lie inside the payload and have no negative
-dimension; duplicate names are rejected by the JSON parser hook. The file is mapped
+dimension; duplicate names are rejected by the JSON parser hook, and so are two entries
+whose byte ranges overlap. The file is mapped
 read-only and tensors are views into the mapping
 (src/kidi/checkpoint/safetensors/mapped.h:388-417). The writer pads the header to 8
 bytes like src/kidi/checkpoint/weights.cpp:148-198.
@@ -109,6 +110,13 @@ class SafetensorsFile:
                     f"{path}: tensor '{name}' spans bytes [{begin}, {end}) but needs "
                     f"{numel * _DTYPES[dtype][2]} inside a payload of {payload}")
             self.entries[name] = TensorEntry(name, dtype, tuple(shape), begin, end)
+        # No two tensors may share payload bytes: sorted by their first byte, each must end
+        # before the next begins (empty tensors take no bytes and cannot overlap anything).
+        spans = sorted((entry.begin, entry.end, entry.name) for entry in self.entries.values()
+                       if entry.end > entry.begin)
+        for (_, end, name), (begin, _, other) in zip(spans, spans[1:]):
+            if begin < end:
+                raise invalid_manifest(f"{path}: tensors '{name}' and '{other}' overlap in the payload")
 
     def names(self) -> Iterable[str]:
         return self.entries.keys()

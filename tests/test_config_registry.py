@@ -93,6 +93,10 @@ def test_registry_chooses_by_architecture_then_model_type():
     assert resolve_architecture(only_type).name == "Qwen3ForCausalLM"
     unknown = dict(TINY_A, architectures=["MambaForCausalLM"], model_type="mamba")
     assert code_of(resolve_architecture, unknown)[0] == ErrorCode.UNSUPPORTED
+    # A model_type alone that nobody registered is an unsupported model, not a broken manifest
+    # (src/kidi/checkpoint/config.cpp:260-264).
+    assert code_of(resolve_architecture, {"model_type": "mamba"})[0] == ErrorCode.UNSUPPORTED
+    assert code_of(resolve_architecture, {"model_type": 7})[0] == ErrorCode.INVALID_MANIFEST
     assert code_of(resolve_architecture, {"hidden_size": 3})[0] == ErrorCode.INVALID_MANIFEST
 
 

@@ -75,6 +75,9 @@ def test_malformed_files_are_rejected(tmp_path):
             tmp_path, {}, b"\0" * 8, raw_header=b'{"t":{"dtype":"F32","shape":[1],"data_offsets":[0,4]},'
                                                 b'"t":{"dtype":"F32","shape":[1],"data_offsets":[4,8]}}'),
         "missing field": lambda: _file_with_header(tmp_path, {"t": {"dtype": "F32", "shape": [1]}}),
+        "overlapping tensors": lambda: _file_with_header(
+            tmp_path, {"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]},
+                       "b": {"dtype": "F32", "shape": [2], "data_offsets": [4, 12]}}, b"\0" * 12, name="overlap.safetensors"),
     }
     for what, make in cases.items():
         path = make()
@@ -121,6 +124,128 @@ def test_dtype_policy():
     assert all(t.dtype == torch.float32 for t in widened.values())
     assert torch.equal(widened["model.layers.0.mlp.down_proj.weight"],
                        tensors["model.layers.0.mlp.down_proj.weight"].float())
+
+
+def test_wider_checkpoints_in_a_bfloat16_engine():
+    """float16 and float32 files: every tensor keeps a width that holds it exactly (32-bit) and
+    a warning names the consequence; on request the matrices are rounded to bfloat16 and the
+    norm vectors stay 32-bit."""
+    for stored in (torch.float16, torch.float32):
+        tensors = {name: tensor.to(stored) for name, tensor in tensors_of(TINY_A).items()}
+        with pytest.warns(UserWarning, match="32-bit kernel"):
+            kept = bind(TINY_A, tensors, torch.bfloat16)
+        assert all(tensor.dtype == torch.float32 for tensor in kept.values())
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("error")
+            cast = bind_parameters(params_of(TINY_A), TensorDict(tensors), engine_dtype=torch.bfloat16, device=CPU,
+                                   cast_matrices=True)
+        for name, tensor in cast.items():
+            assert tensor.dtype == (torch.bfloat16 if tensor.dim() >= 2 else torch.float32), name
+        assert torch.equal(cast["model.layers.0.self_attn.o_proj.weight"],
+                           tensors["model.layers.0.self_attn.o_proj.weight"].to(torch.bfloat16))
+
+
+def test_weight_rules_rename_split_transpose_identical_and_ignore():
+    """Each declarative rule of `WeightRule` fills a parameter from a checkpoint that stores it
+    under another name or in another layout (src/kidi/checkpoint/weights.h:20-31)."""
+    from kidi_b200.parts.spec import ParamSpec, concatenated, identical, renamed, split_from, transposed
+    fused = torch.arange(7 * 4, dtype=torch.float32).reshape(7, 4)
+    stored = {
+        "p.old_name": torch.ones(3, 2),
+        "p.fused": fused,
+        "p.stored_transposed": torch.arange(6, dtype=torch.float32).reshape(2, 3),
+        "p.left": torch.zeros(2, 2), "p.right": torch.ones(2, 3),
+        "p.scale_a": torch.full((1,), 0.5), "p.scale_b": torch.full((1,), 0.5),
+    }
+    params = [
+        ("p.", ParamSpec("new_name", (3, 2), rules=(renamed("old_name", (3, 2)),))),
+        ("p.", ParamSpec("first", (3, 4), rules=(split_from("fused", (7, 4), 0, 0, 3),))),
+        ("p.", ParamSpec("second", (4, 4), rules=(split_from("fused", (7, 4), 0, 3, 4),))),
+        ("p.", ParamSpec("columns", (7, 2), rules=(split_from("fused", (7, 4), 1, 2, 2),))),
+        ("p.", ParamSpec("matrix", (3, 2), rules=(transposed("stored_transposed", (2, 3)),))),
+        ("p.", ParamSpec("wide", (2, 5), rules=(concatenated((("left", (2, 2)), ("right", (2, 3))), axis=1),))),
+        ("p.", ParamSpec("scale", (1,), rules=(identical((("scale_a", (1,)), ("scale_b", (1,)))),))),
+    ]
+    bound = bind_parameters(params, TensorDict(stored), engine_dtype=torch.float32, device=CPU)
+    assert torch.equal(bound["p.new_name"], stored["p.old_name"])
+    assert torch.equal(bound["p.first"], fused[:3]) and torch.equal(bound["p.second"], fused[3:])
+    assert torch.equal(bound["p.columns"], fused[:, 2:4]) and bound["p.columns"].is_contiguous()
+    assert torch.equal(bound["p.matrix"], stored["p.stored_transposed"].t())
+    assert torch.equal(bound["p.wide"], torch.cat([stored["p.left"], stored["p.right"]], dim=1))
+    assert float(bound["p.scale"]) == 0.5
+    # Sources that must be identical and are not: refused.
+    with pytest.raises(KidiError) as caught:
+        bind_parameters(params, TensorDict(dict(stored, **{"p.scale_b": torch.full((1,), 0.25)})),
+                        engine_dtype=torch.float32, device=CPU)
+    assert "same values" in caught.value.message
+    # A tensor nobody uses is unexpected unless a pattern says it may be ignored.
+    extra = dict(stored, **{"p.rotary.inv_freq": torch.zeros(4)})
+    with pytest.raises(KidiError) as caught:
+        bind_parameters(params, TensorDict(extra), engine_dtype=torch.float32, device=CPU)
+    assert "unexpected" in caught.value.message and "p.rotary.inv_freq" in caught.value.message
+    bind_parameters(params, TensorDict(extra), engine_dtype=torch.float32, device=CPU, ignored=[r"^p\.rotary\."])
+    # An absent source of a rule is reported under its own name; a rule that does not make the
+    # parameter's shape is a fault of the part that declared it.
+    lacking = {name: tensor for name, tensor in stored.items() if name != "p.right"}
+    with pytest.raises(KidiError) as caught:
+        bind_parameters(params, TensorDict(lacking), engine_dtype=torch.float32, device=CPU)
+    assert "missing tensors (1): p.right" in caught.value.message
+    with pytest.raises(KidiError) as caught:
+        bind_parameters([("p.", ParamSpec("bad", (5, 5), rules=(transposed("stored_transposed", (2, 3)),)))],
+                        TensorDict(stored), engine_dtype=torch.float32, device=CPU)
+    assert caught.value.code == ErrorCode.INVALID_ARGUMENT
+
+
+def test_parts_name_tensors_they_ignore():
+    """A part's own `ignored_tensors` (relative to its prefix) reach the loader through the model."""
+    from kidi_b200.engine.model import CausalLM
+    from kidi_b200.parts.attention import Attention
+    model = CausalLM(spec_from_config(TINY_A)[2], torch.bfloat16, CPU)
+    assert model.ignored_tensors() == []
+    mixer = model.layers[1].mixer
+    mixer.ignored_tensors = lambda: (r"rotary_emb\.inv_freq$",)
+    patterns = model.ignored_tensors()
+    assert patterns == [r"^model\.layers\.1\.self_attn\.rotary_emb\.inv_freq$"]
+    tensors = dict(tensors_of(TINY_A), **{"model.layers.1.self_attn.rotary_emb.inv_freq": torch.zeros(8)})
+    bind_parameters(model.parameters(), TensorDict(tensors), engine_dtype=torch.bfloat16, device=CPU, ignored=patterns)
+    with pytest.raises(KidiError):
+        bind_parameters(model.parameters(), TensorDict(tensors), engine_dtype=torch.bfloat16, device=CPU)
+
+
+def test_sharded_folder(tmp_path):
+    """A folder whose tensors are spread over shards named by model.safetensors.index.json binds
+    like the single file; a tensor in two shards and a shard path that leaves the folder are
+    refused."""
+    tensors = tensors_of(TINY_B)
+    names = sorted(tensors)
+    cut = len(names) // 3
+    shards = {"model-00001-of-00003.safetensors": names[:cut], "model-00002-of-00003.safetensors": names[cut:2 * cut],
+              "model-00003-of-00003.safetensors": names[2 * cut:]}
+    folder = tmp_path / "sharded"
+    folder.mkdir()
+    weight_map = {}
+    for file, members in shards.items():
+        write_safetensors(str(folder / file), {name: tensors[name] for name in members})
+        weight_map.update({name: file for name in members})
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    checkpoint = Checkpoint(str(folder))
+    assert set(checkpoint.names()) == set(names) and len(checkpoint.files) == 3
+    bound = bind_parameters(params_of(TINY_B), checkpoint, engine_dtype=torch.bfloat16, device=CPU)
+    whole = bind(TINY_B, tensors)
+    assert set(bound) == set(whole) and all(torch.equal(bound[name], whole[name]) for name in whole)
+    checkpoint.close()
+    # The same tensor in two shards.
+    write_safetensors(str(folder / "model-00004-of-00003.safetensors"), {names[0]: tensors[names[0]]})
+    (folder / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": dict(weight_map, extra="model-00004-of-00003.safetensors")}))
+    with pytest.raises(KidiError) as caught:
+        Checkpoint(str(folder))
+    assert "two shards" in caught.value.message
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"x": "../outside.safetensors"}}))
+    with pytest.raises(KidiError) as caught:
+        Checkpoint(str(folder))
+    assert caught.value.code == ErrorCode.INVALID_MANIFEST
 
 
 def test_tied_head_shares_storage_and_conflicts_are_rejected():
