@@ -1,18 +1,24 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the library on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--model 8b|14b|32b] [--impl ours|reference]
 
 A step is one decode step of the batch. The default run is the Qwen3-8B shape (every
 layer size, all 36 layers) with random bfloat16 weights drawn on the device from a
-seed, a batch of 8 sequences with 1,024-token prompts of uniform token ids, then decoding.
-It prints ONE line of JSON:
+seed, a batch of 8 sequences with 1,024-token prompts of uniform token ids, then 512
+decoded tokens each. `--model 14b` and `--model 32b` run the other two shapes with their
+batches of unequal prompts (16 prompts of 128 to 2,048 tokens, 8 prompts of 512 to 8,192
+tokens; 256 steps). It prints ONE line of JSON:
 
 * `value`: decoded tokens a second, timed on the device with CUDA events over exactly K
-  steps after W warm-up steps (tokens selected and fed back on the device);
+  steps after W warm-up steps (tokens selected and fed back on the device): the median
+  of three measured repeats of the same prompts, whose token ids must be identical
+  (the reference's protocol: benchmarks/README.md:27-35, benchmarks/cuda/run.py:48-49);
+* `check`: what vouches for the timed work: the repeats' tokens were identical, and the
+  first 16 tokens of the replayed graph equal those of plain `Engine.step` calls;
 * `e2e`: the same through the Python entry point (`Engine.generate`): host token ids in
-  and out, every step copying its input tokens from pinned host memory and reading its
-  selected tokens back;
+  and out; every step's tokens are read back to pinned host memory for the stop test
+  while the next step, fed on the device, already runs;
 * `prefill`: one 2,048-token prompt: tokens a second, milliseconds, and the fraction of
   the bfloat16 tensor-core peak its FLOPs reach;
 * `roofline`: the decode step's bytes (every weight it uses once, plus the cache of the
@@ -42,8 +48,17 @@ QWEN3_8B = {
     "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0,
     "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 40960, "attention_bias": False,
 }
-PROMPT_TOKENS = 1024
+QWEN3_14B = dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
+# name -> (configuration, batch, (shortest, longest) prompt, decode steps): the benchmark's three shapes
+MODELS = {
+    "8b": ("Qwen3-8B shape", QWEN3_8B, 8, (1024, 1024), 512),
+    "14b": ("Qwen3-14B shape", QWEN3_14B, 16, (128, 2048), 256),
+    "32b": ("Qwen3-32B shape", QWEN3_32B, 8, (512, 8192), 256),
+}
 PREFILL_TOKENS = 2048
+CHECKED_STEPS = 16
+REPEATS = 3
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -121,51 +136,86 @@ def prefill_flops(config: dict, tokens: int) -> float:
     return linear + attention + head
 
 
-def time_decode(engine, sampler, batch: int, steps: int, warmup: int, seed: int, clocks: bool,
-                profile_steps: int = 0):
-    """Device-timed decode: prompts in one step, then `warmup` + `steps` replayed steps
-    with tokens selected and fed back on the device. Returns a dict of measurements."""
+def draw_prompts(vocab: int, batch: int, lengths, seed: int):
+    """`batch` prompts of uniform token ids whose lengths are uniform in [lengths[0], lengths[1]]."""
     import numpy as np
+    generator = np.random.default_rng(seed)
+    sizes = [lengths[0]] * batch if lengths[0] == lengths[1] else generator.integers(lengths[0], lengths[1] + 1, size=batch)
+    return [generator.integers(0, vocab, size=int(size)).tolist() for size in sizes]
+
+
+def time_decode(engine, sampler, prompts, steps: int, warmup: int, clocks: bool, repeats: int = REPEATS,
+                profile_steps: int = 0):
+    """Device-timed decode, `repeats` times over: the prompts in one step, then `warmup` +
+    `steps` replayed steps with tokens selected and fed back on the device, every step's
+    tokens kept on the device. Returns the median repeat's measurements, the tokens of the
+    first repeat and whether every repeat produced the same tokens."""
     import torch
     from kidi_b200 import StepBatch
     from kidi_b200.engine.decode_graph import DecodeSession
-    from kidi_b200.kernels import ops
 
-    generator = np.random.default_rng(seed)
-    prompts = generator.integers(0, engine.vocab_size, size=(batch, PROMPT_TOKENS)).tolist()
-    slots = [engine.acquire() for _ in range(batch)]
-    try:
-        logits = engine.step(StepBatch(slots, prompts, None))
-        first = sampler.select(logits).cpu().tolist()
-        session = DecodeSession(engine, batch, sampler, longest=PROMPT_TOKENS + warmup + steps + 1)
-        session.load(slots, first, [0.0] * batch, list(range(batch)), [1] * batch)
-        session.reserve(warmup + steps)
-        for _ in range(warmup):
-            session.launch()
-        torch.cuda.synchronize()
-        sampler_thread = ClockSampler() if clocks else None
-        if sampler_thread:
-            sampler_thread.start()
-            time.sleep(0.25)
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        begin.record()
-        for _ in range(steps):
-            session.launch()
-        end.record()
-        torch.cuda.synchronize()
-        elapsed_ms = begin.elapsed_time(end)
-        clock_record = sampler_thread.stop() if sampler_thread else None
-        if profile_steps:  # a few more steps inside a profiler range (ncu --profile-from-start off)
-            session.reserve(profile_steps)
-            torch.cuda.profiler.start()
-            for _ in range(profile_steps):
+    batch = len(prompts)
+    longest = max(len(prompt) for prompt in prompts) + warmup + steps + 1
+    session = DecodeSession(engine, batch, sampler, longest=longest)
+    history = torch.zeros((warmup + steps, batch), dtype=torch.int32, device=engine.device)
+    runs, tokens_of_repeat, clock_record = [], [], None
+    for repeat in range(repeats):
+        slots = [engine.acquire() for _ in range(batch)]
+        try:
+            logits = engine.step(StepBatch(slots, prompts, None))
+            first = sampler.select(logits).cpu().tolist()
+            session.load(slots, first, [0.0] * batch, list(range(batch)), [1] * batch)
+            session.reserve(warmup + steps)
+            for step in range(warmup):
                 session.launch()
+                history[step].copy_(session.selected, non_blocking=True)
             torch.cuda.synchronize()
-            torch.cuda.profiler.stop()
-        return {"ms_per_step": elapsed_ms / steps, "tokens_per_s": batch * steps / (elapsed_ms / 1e3),
-                "kernels_per_step": session.kernels_per_step, "clocks": clock_record,
-                "mean_context": PROMPT_TOKENS + warmup + (steps + 1) / 2}
+            sampler_thread = ClockSampler() if clocks and repeat == repeats - 1 else None
+            if sampler_thread:
+                sampler_thread.start()
+                time.sleep(0.25)
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            begin.record()
+            for step in range(steps):
+                session.launch()
+                history[warmup + step].copy_(session.selected, non_blocking=True)   # 4 bytes a sequence, on the device
+            end.record()
+            torch.cuda.synchronize()
+            runs.append(begin.elapsed_time(end) / steps)
+            if sampler_thread:
+                clock_record = sampler_thread.stop()
+            tokens_of_repeat.append([first] + history.cpu().tolist())
+            if profile_steps and repeat == repeats - 1:  # a few more steps inside a profiler range
+                session.reserve(profile_steps)
+                torch.cuda.profiler.start()
+                for _ in range(profile_steps):
+                    session.launch()
+                torch.cuda.synchronize()
+                torch.cuda.profiler.stop()
+        finally:
+            for slot in slots:
+                engine.release(slot)
+    ms = statistics.median(runs)
+    mean_prompt = sum(len(prompt) for prompt in prompts) / batch
+    return {"ms_per_step": ms, "tokens_per_s": batch * 1e3 / ms, "ms_of_repeats": [round(run, 4) for run in runs],
+            "kernels_per_step": session.kernels_per_step, "clocks": clock_record,
+            "mean_context": mean_prompt + warmup + (steps + 1) / 2, "tokens": tokens_of_repeat[0],
+            "repeats_identical": all(tokens == tokens_of_repeat[0] for tokens in tokens_of_repeat)}
+
+
+def tokens_by_plain_steps(engine, sampler, prompts, steps: int):
+    """The same prompts through `Engine.step`, one launch at a time and no graph: the first token
+    of every sequence, then `steps` rows of decoded tokens."""
+    from kidi_b200 import StepBatch
+    slots = [engine.acquire() for _ in prompts]
+    try:
+        tokens = sampler.select(engine.step(StepBatch(slots, prompts, None))).cpu().tolist()
+        rows = [tokens]
+        for _ in range(steps):
+            tokens = sampler.select(engine.step(StepBatch(slots, [[token] for token in tokens], None))).cpu().tolist()
+            rows.append(tokens)
+        return rows
     finally:
         for slot in slots:
             engine.release(slot)
@@ -200,28 +250,29 @@ def time_prefill(engine, seed: int, repeats: int = 5, profile: bool = False):
     return statistics.median(times)
 
 
-def time_end_to_end(engine, batch: int, steps: int, seed: int):
-    """Decode tokens a second through `Engine.generate`: host token ids in and out."""
-    import numpy as np
+def time_end_to_end(engine, prompts, steps: int):
+    """Decode tokens a second through `Engine.generate`: host token ids in and out. Returns
+    the rate, the statistics and the generated tokens."""
     from kidi_b200.engine.generate import GenerationStats
 
-    generator = np.random.default_rng(seed + 1)
-    prompts = generator.integers(0, engine.vocab_size, size=(batch, PROMPT_TOKENS)).tolist()
-    engine.generate(prompts, max_new_tokens=4, ignore_eos=True, max_active=batch)   # captures the graph
+    batch = len(prompts)
+    engine.generate(prompts, max_new_tokens=steps + 1, ignore_eos=True, max_active=batch)   # captures the graph
     stats = GenerationStats()
-    engine.generate(prompts, max_new_tokens=steps + 1, ignore_eos=True, max_active=batch, stats=stats)
-    return batch * stats.decode_steps / (stats.decode_ns / 1e9), stats
+    found = engine.generate(prompts, max_new_tokens=steps + 1, ignore_eos=True, max_active=batch, stats=stats)
+    return batch * stats.decode_steps / (stats.decode_ns / 1e9), stats, found
 
 
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=256)
+    parser.add_argument("--steps", type=int, default=0, help="timed decode steps (default: the model's: 512 / 256)")
     parser.add_argument("--warmup", type=int, default=8)
-    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--batch", type=int, default=0, help="sequences of the batch (default: the model's: 8 / 16 / 8)")
+    parser.add_argument("--model", default="8b", choices=sorted(MODELS), help="which of the benchmark's shapes")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--repeats", type=int, default=REPEATS, help="measured repeats of the decode run (median)")
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
     parser.add_argument("--skip-e2e", action="store_true", help="leave out the end-to-end run (profiling)")
     parser.add_argument("--profile-steps", type=int, default=0,
@@ -239,40 +290,56 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library is single-GPU by design (asked for {args.gpus})")
         return 2
-    if args.steps < 1 or args.warmup < 3:
-        print("bench.py needs --steps >= 1 and --warmup >= 3")
+    title, shape, default_batch, prompt_lengths, default_steps = MODELS[args.model]
+    steps, batch = args.steps or default_steps, args.batch or default_batch
+    if steps < 1 or args.warmup < 3 or args.repeats < 1:
+        print("bench.py needs --steps >= 1, --warmup >= 3 and --repeats >= 1")
         return 2
 
     import torch
     from kidi_b200 import Engine
     from kidi_b200.sampling.sampler import Sampler
 
-    config = dict(QWEN3_8B)
+    config = dict(shape)
     full_layers = config["num_hidden_layers"]
     if args.layers:
         config["num_hidden_layers"] = args.layers
-    largest = max(args.batch, 1 if args.skip_points else 64)
-    per_sequence = PROMPT_TOKENS + args.warmup + args.steps + 2
-    budget = max(largest * (-(-per_sequence // 64) * 64), 4096)
+    points_of = () if args.skip_points or args.model != "8b" else (1, 64)
+    per_sequence = -(-(prompt_lengths[1] + args.warmup + steps + 2) // 64) * 64
+    budget = max(max([batch, *points_of]) * per_sequence, 4096)
     engine = Engine.from_config(config, seed=args.seed, dtype="bfloat16", device="cuda:0", max_tokens=budget)
     sampler = Sampler(args.seed)
     peak = peaks()
 
-    main_run = time_decode(engine, sampler, args.batch, args.steps, args.warmup, args.seed, clocks=True,
+    prompts = draw_prompts(engine.vocab_size, batch, prompt_lengths, args.seed)
+    main_run = time_decode(engine, sampler, prompts, steps, args.warmup, clocks=True, repeats=args.repeats,
                            profile_steps=args.profile_steps)
+    # What vouches for the timed work: the same prompts through plain steps, without the graph.
+    compared = min(CHECKED_STEPS, args.warmup + steps)
+    plain_tokens = tokens_by_plain_steps(engine, sampler, prompts, compared)
+    mismatches = sum(a != b for graph_row, plain_row in zip(main_run["tokens"], plain_tokens)
+                     for a, b in zip(graph_row, plain_row))
+    check = {"repeats": args.repeats, "repeats_identical": main_run["repeats_identical"],
+             "steps_compared_with_plain_steps": compared, "token_mismatches": mismatches,
+             "ms_of_repeats": main_run["ms_of_repeats"]}
     if args.skip_e2e:
         from kidi_b200.engine.generate import GenerationStats
         e2e_value, e2e_stats = 0.0, GenerationStats()
     else:
-        e2e_value, e2e_stats = time_end_to_end(engine, args.batch, args.steps, args.seed)
+        e2e_value, e2e_stats, generated = time_end_to_end(engine, prompts, steps)
+        # The entry point's tokens are the device-timed run's: token n of a sequence is row n of its history.
+        check["e2e_token_mismatches"] = sum(
+            generated[b][n] != main_run["tokens"][n][b] for b in range(batch)
+            for n in range(min(len(generated[b]), len(main_run["tokens"]))))
     if args.profile_prefill:
         time_prefill(engine, args.seed, repeats=1, profile=True)
     points, prefill = {}, None
+    for size in points_of:
+        run = time_decode(engine, sampler, draw_prompts(engine.vocab_size, size, prompt_lengths, args.seed + size),
+                          min(steps, 128), args.warmup, clocks=False, repeats=args.repeats)
+        points[f"decode_b{size}"] = round(run["tokens_per_s"], 1)
+        check[f"decode_b{size}_repeats_identical"] = run["repeats_identical"]
     if not args.skip_points:
-        short = min(args.steps, 128)
-        for batch in (1, 64):
-            run = time_decode(engine, sampler, batch, short, args.warmup, args.seed + batch, clocks=False)
-            points[f"decode_b{batch}"] = round(run["tokens_per_s"], 1)
         prefill_ms = time_prefill(engine, args.seed)
         flops = prefill_flops(config, PREFILL_TOKENS)
         prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "unit": "tokens/s",
@@ -280,27 +347,35 @@ def main() -> int:
                    "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
                    "tflops": round(flops / (prefill_ms / 1e3) / 1e12, 1)}
 
-    achieved = decode_bytes(config, args.batch, main_run["mean_context"]) / (main_run["ms_per_step"] / 1e3) / 1e9
+    achieved = decode_bytes(config, batch, main_run["mean_context"]) / (main_run["ms_per_step"] / 1e3) / 1e9
+    shortest, longest = prompt_lengths
+    prompt_words = f"{shortest}-token prompts" if shortest == longest else f"prompts of {shortest} to {longest} tokens"
     record = {
-        "metric": "decode tokens/s (Qwen3-8B shape, bf16, batch 8, 1024-token prompts)",
+        "metric": f"decode tokens/s ({title}, bf16, batch {batch}, {prompt_words})",
         "value": round(main_run["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
+        "steps": steps, "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0, 0.02) from a seed, uniform token ids", "impl": "ours",
         "config": {
-            "model": "Qwen3-8B shape", "layers": config["num_hidden_layers"], "layers_of_model": full_layers,
+            "model": title, "layers": config["num_hidden_layers"], "layers_of_model": full_layers,
             "hidden_size": config["hidden_size"], "heads": config["num_attention_heads"],
             "kv_heads": config["num_key_value_heads"], "head_dim": config["head_dim"],
             "intermediate_size": config["intermediate_size"], "vocab_size": config["vocab_size"],
             "rope_theta": config["rope_theta"], "rms_norm_eps": config["rms_norm_eps"],
-            "tie_word_embeddings": False, "global_batch": args.batch, "prompt_tokens": PROMPT_TOKENS,
-            "context_per_sequence": 4096, "seq_len": int(main_run["mean_context"]), "parallelism": "single GPU",
-            "l2": "no flush: a step reads ~16 GB, the L2 holds 126 MB", "peaks": peak["source"],
+            "tie_word_embeddings": False, "global_batch": batch,
+            "prompt_tokens": shortest if shortest == longest else f"uniform in [{shortest}, {longest}]",
+            "context_per_sequence": per_sequence if args.model != "8b" else 4096,
+            "seq_len": int(main_run["mean_context"]), "parallelism": "single GPU",
+            "l2": "no flush: a step reads far more than the 126 MB L2 holds", "peaks": peak["source"],
         },
         "clocks": main_run["clocks"],
-        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
-                "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_stats.decode_steps},
-        "gpu_launches": main_run["kernels_per_step"] * args.steps,
+        "checked": bool(main_run["repeats_identical"] and mismatches == 0), "check": check,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": round(e2e_stats.host_to_device_bytes / max(1, e2e_stats.decode_steps), 1),
+                "d2h_bytes_per_step": 4 * batch, "steps": e2e_stats.decode_steps,
+                "note": "a step's input tokens are its predecessor's output on the device; the host copies the "
+                        "batch's tables up when decoding starts and reads every step's tokens back"},
+        "gpu_launches": main_run["kernels_per_step"] * steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4), "of": peak["source"]},
     }

@@ -19,7 +19,13 @@ what its mixer needs:
   `ceil(window / page_size)` pages at most, and token `u` lives in ring row
   `u mod (ring_pages * page_size)`.
 * `StateRequest(shape, dtype)`: per-sequence state of fixed size, stored
-  `[entries, slots, *shape]` and zeroed when a slot is handed out.
+  `[entries, slots + 1, *shape]` and zeroed when a slot is handed out.
+
+The last row of every state tensor and of every block table belongs to the padding slot
+(`padding_slot`, one past the slots that are handed out): a captured decode step has a
+fixed number of rows, and the sequences beyond the live ones carry that slot, so that a
+mixer which updates "the state of every sequence of the step" writes, for them, where
+nothing is ever read.
 
 The budget is a number of tokens (`max_tokens`): the most that live sequences hold at
 any time, each sequence's count rounded up to a whole page. Slots and pages are
@@ -76,18 +82,36 @@ class KVGroup:
         self.n_pages = n_pages
         self.pool = IdAllocator(n_pages, "cache page")
         shape = (len(entries), n_pages, request.kv_heads, page_size, request.head_dim)
-        # Zero-filled: rows of a page beyond a sequence's length are loaded with their
-        # tile and multiplied by a zero probability, so they have to be finite.
+        # Rows of a page beyond a sequence's length are loaded with their tile and multiplied by
+        # a zero probability, so the values there have to be finite (keys need not be: a masked
+        # score is replaced whatever it was). The pools start zero-filled, and the values of a
+        # page that has been used are cleared when it is handed out again (`clear_used`): what
+        # an earlier sequence left, were it ever an infinity or a NaN, must not reach the next.
         self.keys = torch.zeros(shape, dtype=dtype, device=device)
         self.values = torch.zeros(shape, dtype=dtype, device=device)
-        self.table_host = np.zeros((n_slots, self.pages_per_sequence), dtype=np.int32)
-        self.table = torch.zeros((n_slots, self.pages_per_sequence), dtype=torch.int32, device=device)
+        self.used = np.zeros(n_pages, dtype=bool)       # pages that have been handed out before
+        # One row more than there are slots: the padding slot's (all zeros, never filled in).
+        self.table_host = np.zeros((n_slots + 1, self.pages_per_sequence), dtype=np.int32)
+        self.table = torch.zeros((n_slots + 1, self.pages_per_sequence), dtype=torch.int32, device=device)
         self.pages: Dict[int, List[int]] = {}
         self._dirty: set = set()
 
     @property
     def ring_tokens(self) -> int:
         return self.ring_pages * self.page_size
+
+    def clear_used(self, pages: Sequence[int]) -> None:
+        """Clears the values of those of `pages` that were handed out before, as runs of
+        consecutive pages (on the current stream, before the step that writes them)."""
+        again = sorted(page for page in pages if self.used[page])
+        self.used[list(pages)] = True
+        start = 0
+        while start < len(again):
+            stop = start + 1
+            while stop < len(again) and again[stop] == again[stop - 1] + 1:
+                stop += 1
+            self.values[:, again[start]:again[stop - 1] + 1].zero_()
+            start = stop
 
     def pages_for(self, length: int) -> int:
         needed = -(-length // self.page_size)
@@ -102,7 +126,8 @@ class StateGroup:
                  device: torch.device):
         self.request = request
         self.entries = entries
-        self.storage = torch.zeros((len(entries), n_slots, *request.shape), dtype=request.dtype or dtype,
+        # One row more than there are slots: the padding slot's, which anything may be written to.
+        self.storage = torch.zeros((len(entries), n_slots + 1, *request.shape), dtype=request.dtype or dtype,
                                    device=device)
 
     def bytes(self) -> int:
@@ -154,6 +179,7 @@ class SequenceCache:
         n_pages = self.max_tokens // page_size
         self.n_slots = min(n_pages, max_slots) if max_slots else n_pages
         self.slots = IdAllocator(self.n_slots, "cache slot")
+        self.padding_slot = self.n_slots          # never handed out: what padding sequences of a captured step carry
         self.lengths: Dict[int, int] = {}
         self.dtype, self.device = dtype, device
         cache_from = list(cache_from) if cache_from is not None else [None] * len(requests)
@@ -190,7 +216,8 @@ class SequenceCache:
     # ------------------------------------------------------------------ views
     def views(self, entry: int) -> List[object]:
         """The views of schedule entry `entry`, in the order of its requests: a
-        `KVView` per `KVRequest`, a tensor `[slots, *shape]` per `StateRequest`."""
+        `KVView` per `KVRequest`, a tensor `[slots + 1, *shape]` per `StateRequest` (its last
+        row is the padding slot's)."""
         source = self._cache_from[entry]
         if source is not None:
             if source >= entry or self._cache_from[source] is not None:
@@ -248,6 +275,7 @@ class SequenceCache:
                 if extra > 0:
                     first = len(held)
                     held.extend(group.pool.acquire_many(extra))
+                    group.clear_used(held[first:])
                     group.table_host[slot, first:len(held)] = held[first:]
                     group._dirty.add(slot)
 

@@ -150,9 +150,13 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const void* we
     if (vectors && hidden == THREADS * 4 * CHUNKS)                                                            \
         return kidi_launch_small(add_rmsnorm_vector_kernel<TD, TW, TY, THREADS, CHUNKS>, rows, THREADS, 0, stream, \
                            residual, (const TD*)delta, (const TW*)weight, (TY*)y, row_index, eps, write_residual);
-    KIDI_VECTOR_CASE(1)
+    KIDI_VECTOR_CASE(1)     // every multiple of 1024 up to 8192 elements
     KIDI_VECTOR_CASE(2)
+    KIDI_VECTOR_CASE(3)
     KIDI_VECTOR_CASE(4)
+    KIDI_VECTOR_CASE(5)
+    KIDI_VECTOR_CASE(6)
+    KIDI_VECTOR_CASE(7)
     KIDI_VECTOR_CASE(8)
 #undef KIDI_VECTOR_CASE
     const size_t shared = (size_t)hidden * sizeof(float);
@@ -266,5 +270,31 @@ KIDI_API int kidi_silu_gate(const void* gate_up, void* out, int dtype, int rows,
         return kidi_launch(silu_gate_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total,
                            inter);
     }
+    return KIDI_REFUSED_DTYPE;
+}
+
+// y[r, c] += bias[c]: the bias of a product that the vendor library computed (this package's
+// own products add it in their epilogues).
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, long long total, int features,
+                                long long ldy) {
+    pdl_prologue();
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const long long row = index / features;
+    const int c = (int)(index - row * features);
+    y[row * ldy + c] = from_float<T>(to_float(y[row * ldy + c]) + bias[c]);
+}
+
+KIDI_API int kidi_add_bias(void* y, int dtype, const float* bias, int rows, int features, long long ldy,
+                           cudaStream_t stream) {
+    const long long total = (long long)rows * features;
+    if (total <= 0) return 0;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (dtype == KIDI_F32)
+        return kidi_launch(add_bias_kernel<float>, blocks, threads, 0, stream, (float*)y, bias, total, features, ldy);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(add_bias_kernel<bf16>, blocks, threads, 0, stream, (bf16*)y, bias, total, features, ldy);
     return KIDI_REFUSED_DTYPE;
 }

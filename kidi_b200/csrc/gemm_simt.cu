@@ -16,7 +16,7 @@ constexpr int PAD = 4;
 template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int M, int N, int K,
-                 long long ldx, long long ldw, long long ldy) {
+                 long long ldx, long long ldw, long long ldy, const float* __restrict__ bias) {
     __shared__ float xs[TILE_K][TILE + PAD];
     __shared__ float ws[TILE_K][TILE + PAD];
     pdl_prologue();
@@ -61,27 +61,29 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restr
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < N) y[m * ldy + n] = from_float<TY>(acc[i][j]);
+            if (n < N) y[m * ldy + n] = from_float<TY>(bias ? acc[i][j] + bias[n] : acc[i][j]);
         }
     }
 }
 
 template <typename TX, typename TW, typename TY>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw, long long ldy,
-           cudaStream_t stream) {
+           const float* bias, cudaStream_t stream) {
     dim3 grid((N + TILE - 1) / TILE, (M + TILE - 1) / TILE);
     return kidi_launch(gemm_simt_kernel<TX, TW, TY>, grid, 256, 0, stream, (const TX*)x, (const TW*)w, (TY*)y, M, N, K,
-                       ldx, ldw, ldy);
+                       ldx, ldw, ldy, bias);
 }
 }  // namespace
 
+// `bias` (float32 [N], or null) is added to every row after the chain of multiply-adds
+// (the reference's Linear with bias, src/kidi/layers/linear.cpp:181-190).
 KIDI_API int kidi_gemm_simt(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype, int M, int N,
-                            int K, long long ldx, long long ldw, long long ldy, cudaStream_t stream) {
+                            int K, long long ldx, long long ldw, long long ldy, const float* bias, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (M + TILE - 1) / TILE > 65535) return KIDI_REFUSED_SIZE;
 #define KIDI_CASE(X, TX, W, TW, Y, TY)                                 \
     if (x_dtype == X && w_dtype == W && y_dtype == Y)                  \
-        return launch<TX, TW, TY>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+        return launch<TX, TW, TY>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream);
     KIDI_CASE(KIDI_F32, float, KIDI_F32, float, KIDI_F32, float)
     KIDI_CASE(KIDI_F32, float, KIDI_F32, float, KIDI_BF16, bf16)
     KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16, KIDI_F32, float)

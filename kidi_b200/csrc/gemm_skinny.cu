@@ -52,7 +52,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 template <int MT, int NT, int UNROLL, bool GATED, typename TY>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* __restrict__ y, int M, int N, int K,
-                   long long ldx, long long ldw, long long ldy) {
+                   long long ldx, long long ldw, long long ldy, const float* __restrict__ bias) {
     extern __shared__ float partial[];  // [WARPS][MT*16][NT*8]
     constexpr int ROWS = MT * 16, COLS = NT * 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -185,6 +185,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* _
 #pragma unroll
             for (int v = 0; v < WARPS; ++v) up += partial[((long long)v * ROWS + (MT == 1 ? 8 : 16) + r) * COLS + m];
             sum = sum / (1.0f + expf(-sum)) * up;
+        } else if (bias) {
+            sum += bias[n0 + r];
         }
         y[m * ldy + n0 + r] = from_float<TY>(sum);
     }
@@ -192,7 +194,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* _
 
 template <int MT, int NT, int UNROLL, bool GATED, typename TY>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw, long long ldy,
-           cudaStream_t stream) {
+           const float* bias, cudaStream_t stream) {
     const int span = GATED ? (MT == 1 ? 8 : 16) : MT * 16;
     const size_t shared = (size_t)WARPS * MT * 16 * NT * 8 * sizeof(float);
     auto kernel = gemm_skinny_kernel<MT, NT, UNROLL, GATED, TY>;
@@ -201,16 +203,16 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, long long
         if (status != cudaSuccess) return (int)status;
     }
     return kidi_launch(kernel, (N + span - 1) / span, WARPS * 32, shared, stream, (const bf16*)x, (const bf16*)w,
-                       (TY*)y, M, N, K, ldx, ldw, ldy);
+                       (TY*)y, M, N, K, ldx, ldw, ldy, bias);
 }
 
 template <int MT, bool GATED, typename TY>
 int by_batch(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw, long long ldy,
-             cudaStream_t stream) {
-    if (M <= 8) return launch<MT, 1, (MT == 1 ? 8 : 4), GATED, TY>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
-    if (M <= 16) return launch<MT, 2, (MT == 1 ? 8 : 4), GATED, TY>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
-    if (M <= 32) return launch<MT, 4, (MT == 1 ? 4 : 2), GATED, TY>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
-    return launch<MT, 8, 2, GATED, TY>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+             const float* bias, cudaStream_t stream) {
+    if (M <= 8) return launch<MT, 1, (MT == 1 ? 8 : 4), GATED, TY>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream);
+    if (M <= 16) return launch<MT, 2, (MT == 1 ? 8 : 4), GATED, TY>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream);
+    if (M <= 32) return launch<MT, 4, (MT == 1 ? 4 : 2), GATED, TY>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream);
+    return launch<MT, 8, 2, GATED, TY>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream);
 }
 }  // namespace
 
@@ -219,25 +221,28 @@ int by_batch(const void* x, const void* w, void* y, int M, int N, int K, long lo
 // multiples of 8 and base pointers 16-byte aligned).
 // gated != 0: w is [2N, K] (N gate rows then N up rows), y is [M, N] = silu(gate) * up.
 // row_tiles: 1 or 2 tiles of 16 weight rows per block (the gated form uses 2).
+// bias: float32 [N] added to every row, or null (not with the gate).
 KIDI_API int kidi_gemm_skinny(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K, long long ldx,
-                              long long ldw, long long ldy, int gated, int row_tiles, cudaStream_t stream) {
+                              long long ldw, long long ldy, int gated, int row_tiles, const float* bias,
+                              cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
         return KIDI_REFUSED_SIZE;
     if (gated) {
         if (y_dtype != KIDI_BF16) return KIDI_REFUSED_DTYPE;
+        if (bias) return KIDI_REFUSED_SIZE;
         // Up to seven batch rows: eight gate and eight up rows per tile (measured on the 201 MB
         // gate/up weight of the benchmark's model: 32.7 against 35.6 us at one row, 36.7 against
         // 38.1 at six, equal at eight); more rows: sixteen and sixteen.
         if (row_tiles == 1 || (M < 8 && row_tiles != 2))
-            return by_batch<1, true, bf16>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
-        return by_batch<2, true, bf16>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+            return by_batch<1, true, bf16>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream);
+        return by_batch<2, true, bf16>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream);
     }
     if (y_dtype == KIDI_BF16)
-        return row_tiles == 2 ? by_batch<2, false, bf16>(x, w, y, M, N, K, ldx, ldw, ldy, stream)
-                              : by_batch<1, false, bf16>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+        return row_tiles == 2 ? by_batch<2, false, bf16>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream)
+                              : by_batch<1, false, bf16>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream);
     if (y_dtype == KIDI_F32)
-        return row_tiles == 2 ? by_batch<2, false, float>(x, w, y, M, N, K, ldx, ldw, ldy, stream)
-                              : by_batch<1, false, float>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+        return row_tiles == 2 ? by_batch<2, false, float>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream)
+                              : by_batch<1, false, float>(x, w, y, M, N, K, ldx, ldw, ldy, bias, stream);
     return KIDI_REFUSED_DTYPE;
 }

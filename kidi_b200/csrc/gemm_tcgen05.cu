@@ -118,6 +118,7 @@ struct Params {
     float* workspace;      // [units][BM][BN] partial tiles (split-K only)
     int* counters;         // [feature tiles * token tiles], zero between calls (the kernel leaves them zero)
     int* error;            // set to a non-zero code when a bounded wait ran out
+    const float* bias;     // [features] added to every token's row, or null (not with the gate)
     long long ldy;
     int tokens, features;  // features: width of y (for the gated form the weight has 2 * features rows)
     int k_blocks;          // ceil(K / 64)
@@ -283,10 +284,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                 } else if (f0 + row < p.features) {
+                    const float shift = p.bias ? p.bias[f0 + row] : 0.f;
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int token = t0 + c + i;
-                        if (token < p.tokens) y[token * p.ldy + f0 + row] = from_float<TY>(v[i]);
+                        if (token < p.tokens) y[token * p.ldy + f0 + row] = from_float<TY>(v[i] + shift);
                     }
                 }
             }
@@ -374,10 +376,11 @@ KIDI_API long long kidi_gemm_tcgen05_workspace(int tokens, int features, int spl
 
 // x [tokens, K] and w [features (2 * features when gated), K] bfloat16, rows 16-byte
 // aligned; y [tokens, features] bfloat16 or float32. `workspace`, `counters` (zeroed
-// once by the caller; the kernel leaves them zero) and `error` are the caller's.
+// once by the caller; the kernel leaves them zero) and `error` are the caller's. `bias`
+// (float32 [features], or null) is added to every row.
 KIDI_API int kidi_gemm_tcgen05(const void* x, const void* w, void* y, int y_dtype, int tokens, int features, int K,
                                long long ldx, long long ldw, long long ldy, int gated, int splits, float* workspace,
-                               int* counters, int* error, cudaStream_t stream) {
+                               int* counters, int* error, const float* bias, cudaStream_t stream) {
     if (tokens <= 0 || features <= 0) return 0;
     if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || splits < 1)
         return KIDI_REFUSED_SIZE;
@@ -388,6 +391,7 @@ KIDI_API int kidi_gemm_tcgen05(const void* x, const void* w, void* y, int y_dtyp
     p.workspace = workspace;
     p.counters = counters;
     p.error = error;
+    p.bias = bias;
     p.ldy = ldy;
     p.tokens = tokens;
     p.features = features;
@@ -405,6 +409,7 @@ KIDI_API int kidi_gemm_tcgen05(const void* x, const void* w, void* y, int y_dtyp
     if (status) return status;
     if (gated) {
         if (y_dtype != KIDI_BF16) return KIDI_REFUSED_DTYPE;
+        if (bias) return KIDI_REFUSED_SIZE;
         return by_tokens<true, bf16>(bn, map_w, map_x, p, token_tiles, stream);
     }
     if (y_dtype == KIDI_BF16) return by_tokens<false, bf16>(bn, map_w, map_x, p, token_tiles, stream);

@@ -9,11 +9,19 @@ step's integer tables, the sampling parameters and the selected tokens. The capt
 graph runs the model's ordinary forward pass over those buffers, selects a token per
 row on the device, and advances tokens and positions for the next step. Between
 replays the host only rewrites the buffers (one copy) when the set of live sequences
-changes, and reads the selected tokens back.
+changes, and reads the selected tokens back. The tokens a step selects are its
+successor's inputs where they lie on the device, so the host may submit the next step
+before it has read the last one's tokens (the reference's decode-ahead with device tokens
+and an asynchronous read-back into pinned memory, src/kidi/inference/generator.cpp:1044-1093).
 
 Rows beyond the live sequences are padding: their `row_seq` is -1, so they write
 nothing to the cache and attend to nothing; what the other kernels compute for them is
-never read.
+never read. The rule for every part that keeps something per sequence: a row whose
+`row_seq` is negative touches neither keys, values nor state of any slot. As a net
+under that rule the padding sequences carry the cache's padding slot in `seq_slot`
+(the last row of every state tensor and block table), never a slot that a live
+sequence may hold. The host tables of the step's `plan` are placeholders here (the
+graph is captured once): a part that is to run in a captured step reads `ctx.tables`.
 """
 from __future__ import annotations
 
@@ -24,13 +32,13 @@ import numpy as np
 import torch
 
 from ..errors import KidiError, invalid_argument
-from ..kernels import attention as attention_kernels
 from ..kernels import ops
 from .plan import StepPlan
 
 
 class DecodeSession:
     FIELDS = ("tokens", "row_seq", "row_pos", "seq_slot", "seq_start", "seq_len", "seq_row0", "want_rows", "steps")
+    READBACK_DEPTH = 4
 
     def __init__(self, engine, capacity: int, sampler, *, longest: Optional[int] = None):
         from .engine import DeviceTables, StepContext
@@ -54,11 +62,14 @@ class DecodeSession:
         self._temperature_at = base
         self._keys_at = base + padded
         self.selected = torch.zeros(capacity, dtype=torch.int32, device=device)
-        self.selected_host = torch.zeros(capacity, dtype=torch.int32).pin_memory()
+        # Read-back buffers in pinned memory, used in turn: a step's tokens stay readable while
+        # the steps submitted after it run.
+        self._readback = [torch.zeros(capacity, dtype=torch.int32).pin_memory() for _ in range(self.READBACK_DEPTH)]
+        self._readback_views = [buffer.numpy() for buffer in self._readback]
+        self._readback_done = [torch.cuda.Event() for _ in range(self.READBACK_DEPTH)]
+        self._submitted = 0            # steps submitted since the session was made
         self.tokens_host = torch.zeros(capacity, dtype=torch.int32).pin_memory()
         self._tokens_host_view = self.tokens_host.numpy()
-        self._selected_host_view = self.selected_host.numpy()
-        self._reserved_ahead = False
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.live = 0
@@ -66,16 +77,13 @@ class DecodeSession:
         self._plan = StepPlan(
             n_rows=capacity, n_seqs=capacity, n_want=capacity, max_new=1,
             max_total=longest or engine.spec.max_positions, is_decode=True,
-            tokens=rows * 0, row_seq=rows, row_pos=rows * 0, seq_slot=rows * 0, seq_start=rows * 0,
+            tokens=rows * 0, row_seq=rows, row_pos=rows * 0, seq_slot=rows * 0 + engine.cache.padding_slot,
+            seq_start=rows * 0,
             seq_len=rows * 0 + 1, seq_row0=rows, want_rows=rows)
+        # Launch dimensions that depend on the sequence length (the key splits of decode
+        # attention, chosen by each attention part for its own geometry) are fixed when the graph
+        # is captured, from `max_total`: the longest sequence this session may come to hold.
         self._context = StepContext(self._plan, self.tables, engine.cache, engine.dtype, device, engine._workspaces)
-        widest = _widest_decode(engine)
-        if widest is not None:
-            # The number of key splits is a launch dimension: it is fixed when the graph is
-            # captured, from the longest sequence this session may come to hold.
-            heads, head_dim = widest
-            self._context.decode_splits = attention_kernels.decode_splits(
-                capacity, heads, self._plan.max_total, device, head_dim)
         self._stream = torch.cuda.Stream(device=device)
 
     # ------------------------------------------------------------------ set-up
@@ -102,7 +110,7 @@ class DecodeSession:
         field("row_seq")[:live] = np.arange(live, dtype=np.int32)
         field("row_pos")[:] = 0
         field("row_pos")[:live] = starts
-        field("seq_slot")[:] = 0
+        field("seq_slot")[:] = cache.padding_slot
         field("seq_slot")[:live] = slots
         field("seq_start")[:] = 0
         field("seq_start")[:live] = starts
@@ -116,11 +124,11 @@ class DecodeSession:
         host[self._keys_at:self._keys_at + 2 * capacity].view(np.int64)[:] = 0
         host[self._keys_at:self._keys_at + 2 * live].view(np.int64)[:] = keys
         self.buffer.copy_(self.staging, non_blocking=True)
+        self.uploaded_bytes = self.staging.numel() * self.staging.element_size()
         torch.cuda.current_stream().synchronize()  # the staging buffer may be rewritten after this
         self.live = live
         self.slots = list(slots)
         self.positions = list(starts)
-        self._reserved_ahead = False
 
     # -------------------------------------------------------------------- step
     def _forward(self) -> None:
@@ -136,6 +144,8 @@ class DecodeSession:
         saved = self.buffer.clone()
         begin = self._offsets["row_seq"][0]
         self.buffer[begin:begin + self.capacity] = -1
+        begin = self._offsets["seq_slot"][0]
+        self.buffer[begin:begin + self.capacity] = self.engine.cache.padding_slot
         torch.cuda.synchronize(self.engine.device)
         with torch.cuda.stream(self._stream):
             self._forward()
@@ -178,34 +188,33 @@ class DecodeSession:
         self.positions = [position + 1 for position in self.positions]
         self.engine.cache.commit(list(zip(self.slots, self.positions)))
 
-    def step(self, tokens: Optional[Sequence[int]] = None) -> List[int]:
-        """One decode step; returns the selected token of every live sequence. With
-        `tokens` (host integers, one per live sequence) the step's inputs are copied from
-        pinned host memory first; without, the tokens selected by the previous step are
-        used where they lie on the device."""
-        if not self._reserved_ahead:
-            self.reserve(1)
-        self._reserved_ahead = False
+    def submit(self, tokens: Optional[Sequence[int]] = None) -> int:
+        """Submits one decode step without waiting for it and returns a ticket for `read`.
+        Without `tokens` the step's inputs are the tokens the previous step selected, where
+        they lie on the device; with `tokens` (host integers, one per live sequence) they are
+        copied from pinned host memory first. At most READBACK_DEPTH - 1 steps may be
+        submitted beyond the last one read."""
+        self.reserve(1)
         if tokens is not None:
             self._tokens_host_view[:self.live] = tokens
             self.tables.tokens[:self.live].copy_(self.tokens_host[:self.live], non_blocking=True)
         self.launch()
-        self.selected_host.copy_(self.selected, non_blocking=True)
-        # While the device runs the step, the host makes room for the next one (a sequence
-        # that turns out to have ended gives the room back with its slot). Where there is no
-        # room to take ahead of time, the next step asks again and reports it.
-        try:
-            self.reserve(1)
-            self._reserved_ahead = True
-        except KidiError:
-            pass
-        torch.cuda.current_stream().synchronize()
-        return self._selected_host_view[:self.live].tolist()
+        ticket = self._submitted
+        self._submitted += 1
+        turn = ticket % self.READBACK_DEPTH
+        self._readback[turn].copy_(self.selected, non_blocking=True)
+        self._readback_done[turn].record()
+        return ticket
 
+    def read(self, ticket: int) -> List[int]:
+        """Waits for the step of `ticket` and returns the token it selected for every live
+        sequence."""
+        if not self._submitted - self.READBACK_DEPTH < ticket < self._submitted:
+            raise invalid_argument("this step's tokens are no longer kept (too many steps were submitted since)")
+        turn = ticket % self.READBACK_DEPTH
+        self._readback_done[turn].synchronize()
+        return self._readback_views[turn][:self.live].tolist()
 
-def _widest_decode(engine):
-    """The (key/value head count, head width) that decides how decode attention is split:
-    those of the attention cache with the fewest key/value heads (None when no layer has
-    an attention cache)."""
-    shapes = [(group.request.kv_heads, group.request.head_dim) for group in engine.cache.kv_groups]
-    return min(shapes) if shapes else None
+    def step(self, tokens: Optional[Sequence[int]] = None) -> List[int]:
+        """One decode step, waited for: the selected token of every live sequence."""
+        return self.read(self.submit(tokens))

@@ -41,19 +41,13 @@ class DeviceTables:
 
 
 class StepContext:
-    """What parts see of a step."""
+    """What parts see of a step: the host tables (`plan`), the device tables (`tables`), the
+    cache, the engine's element type and device, and scratch memory. It knows no kind of part."""
 
     def __init__(self, plan: StepPlan, tables: DeviceTables, cache: SequenceCache, dtype: torch.dtype,
                  device: torch.device, workspaces: Optional[Dict[str, torch.Tensor]] = None):
         self.plan, self.tables, self.cache, self.dtype, self.device = plan, tables, cache, dtype, device
         self._workspaces = workspaces if workspaces is not None else {}
-
-    def attention(self, qkv, out, **arguments) -> None:
-        attention_kernels.run(self, qkv, out, **arguments)
-
-    def fuses_rotation(self, qkv, **arguments) -> bool:
-        """Whether `attention` can do norm, rotation and the cache write of this step itself."""
-        return attention_kernels.fuses_rotation(self.plan, qkv, **arguments)
 
     def workspace(self, name: str, count: int, zero: bool = False) -> torch.Tensor:
         """Scratch memory of at least `count` 32-bit elements that kernels of one step may
@@ -175,14 +169,15 @@ class Engine:
                  max_tokens: Optional[Sequence[Optional[int]]] = None, stats=None, detailed: bool = False):
         """Generates for every prompt (lists of token ids, host integers) and returns the
         new token ids of each, in order; with `detailed`, `Generation` records instead.
-        The model's own end tokens stop a sequence unless `ignore_eos` is set."""
+        The model's own end tokens stop a sequence unless `ignore_eos` is set. `max_active`
+        bounds the sequences of a batch (0: as many as the cache has slots and tokens for)."""
         from ..sampling.sampler import Sampler
-        from .generate import DEFAULT_MAX_ACTIVE, EngineBackend, GenerationOptions, generate
+        from .generate import EngineBackend, GenerationOptions, generate
         with torch.cuda.device(self.device):
             options = GenerationOptions(
                 max_new_tokens=max_new_tokens, context_size=context_size, prefill_chunk_size=prefill_chunk_size,
                 temperature=temperature, seed=seed, ignore_eos=ignore_eos, stop_ids=tuple(stop_ids),
-                max_active=max_active or DEFAULT_MAX_ACTIVE, use_graph=use_graph)
+                max_active=max_active or self.cache.n_slots, use_graph=use_graph)
             key = (seed, use_graph)
             backend = self._backends.get(key)
             if backend is None:

@@ -15,6 +15,15 @@ its limits (src/kidi/inference/generator.cpp:136-140,438-445: `maximum_new_token
 the default of 8192, `context_size` 0 means min(max_position_embeddings, 16384), a prompt
 and its new tokens must fit the context). Unlike the reference, which prefills each
 prompt alone (src/kidi/inference/generator.cpp:573-604), the prompts of a batch share one step.
+
+Decoding runs one step ahead of the host (the reference's decode-ahead,
+src/kidi/inference/generator.cpp:1044-1093): a step's selected tokens are its successor's
+inputs where they lie on the device, so the loop submits step n+1 before it reads the
+tokens of step n, and the read-back and the stop test overlap the device's work. A step
+is only submitted ahead when no sequence can reach its length limit in the step before
+it; when a stop token ends a sequence after all, the step that already ran is still
+right for the others (a sequence's tokens do not depend on its neighbours), so its
+tokens are kept for them and only the ended sequence's extra token is dropped.
 """
 from __future__ import annotations
 
@@ -28,7 +37,9 @@ from .search import Generation, SequenceState, plan_batches
 
 DEFAULT_MAX_NEW_TOKENS = 8192
 DEFAULT_CONTEXT_LIMIT = 16384
-DEFAULT_MAX_ACTIVE = 4
+DEFAULT_MAX_ACTIVE = 4   # the command line's default, as the reference's (src/kidi/cli/main.cpp:905-958);
+                         # `Engine.generate` without `max_active` takes as many as the cache has slots for
+MAX_KEPT_SESSIONS = 6    # captured decode steps an engine keeps (the least recently used goes first)
 
 
 @dataclasses.dataclass
@@ -54,13 +65,16 @@ class GenerationStats:
     decode_ns: int = 0
     time_to_first_token_ns: int = 0
     generation_ns: int = 0
+    host_to_device_bytes: int = 0   # copied up while decoding (the tables of a batch, when a session is loaded)
 
 
 class Backend:
     """What the loop needs from an engine; tests substitute a fake one.
 
-    acquire() -> slot; release(slot); prefill(slots, chunks, want_last) -> selected tokens
-    or None; open_decode(slots, tokens, ...) -> object with step() -> tokens."""
+    acquire() -> slot; release(slot); prefill(slots, chunks, select, ...) -> the first
+    tokens of the sequences whose prompt the chunk ends; open_decode(slots, tokens, ...) ->
+    a session with submit() -> ticket (one more step for every sequence, not waited for,
+    fed with the tokens of the step before it) and read(ticket) -> that step's tokens."""
 
 
 class EngineBackend(Backend):
@@ -97,29 +111,41 @@ class EngineBackend(Backend):
         capacity = 1
         while capacity < len(slots):
             capacity *= 2
-        session = self._sessions.get(capacity)
+        longest = min(longest, self.max_positions)
+        # A captured step freezes launch choices that depend on the longest sequence (the key
+        # splits of decode attention): a call with other choices gets a capture of its own.
+        key = (capacity, self.engine.model.launch_signature(capacity, longest))
+        session = self._sessions.pop(key, None)
         if session is None:
-            session = DecodeSession(self.engine, capacity, self.sampler, longest=min(longest, self.max_positions))
-            self._sessions[capacity] = session
+            session = DecodeSession(self.engine, capacity, self.sampler, longest=longest)
+            while len(self._sessions) >= MAX_KEPT_SESSIONS:
+                self._sessions.pop(next(iter(self._sessions)))
+        self._sessions[key] = session          # most recently used last
         session.load(slots, tokens, temperature, keys, steps)
         return session
 
 
 class _EagerDecode:
-    """Decode steps through `Engine.step`, one launch at a time (no graph)."""
+    """Decode steps through `Engine.step`, one launch at a time (no graph). A submitted step
+    runs when its tokens are asked for: every step needs its predecessor's tokens on the host."""
 
     def __init__(self, backend, slots, tokens, temperature, keys, steps):
         self.backend, self.slots, self.tokens = backend, list(slots), list(tokens)
         self.temperature, self.keys, self.steps = list(temperature), list(keys), list(steps)
+        self._submitted, self._results = 0, {}
 
-    def step(self, tokens: Optional[Sequence[int]] = None) -> List[int]:
+    def submit(self) -> int:
+        self._submitted += 1
+        return self._submitted - 1
+
+    def read(self, ticket: int) -> List[int]:
         engine, sampler = self.backend.engine, self.backend.sampler
-        if tokens is not None:
-            self.tokens = list(tokens)
-        logits = engine.step(StepBatch(self.slots, [[token] for token in self.tokens], None))
-        self.tokens = sampler.select_host(logits, self.temperature, self.keys, self.steps)
-        self.steps = [step + 1 for step in self.steps]
-        return list(self.tokens)
+        while len(self._results) <= ticket:
+            logits = engine.step(StepBatch(self.slots, [[token] for token in self.tokens], None))
+            self.tokens = sampler.select_host(logits, self.temperature, self.keys, self.steps)
+            self.steps = [step + 1 for step in self.steps]
+            self._results[len(self._results)] = list(self.tokens)
+        return self._results[ticket]
 
 
 def generate(backend: Backend, prompts: Sequence[Sequence[int]], options: GenerationOptions,
@@ -193,25 +219,41 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], options: Genera
                 first_token_seen = True
             for i in [i for i in members if states[i].finished]:
                 finish(i)
-            # ---- one token per live sequence per step; the session is reopened when a sequence leaves
+            # ---- one token per live sequence per step, submitted one step ahead of the host;
+            # the session is reopened when a sequence leaves
             tick = time.perf_counter_ns()
             live = [i for i in members if not states[i].finished]
-            session = None
+            session, ticket = None, None
             while live:
                 if session is None:
                     longest = max(len(prompts[i]) + limits[i] for i in live)
                     session = backend.open_decode([slots[i] for i in live], [states[i].token for i in live],
                                                   [options.temperature] * len(live), live,
                                                   [states[i].steps for i in live], longest)
-                chosen = session.step([states[i].token for i in live])
+                    stats.host_to_device_bytes += getattr(session, "uploaded_bytes", 0)
+                    ticket = session.submit()
+                # The step ahead: only if the step in flight cannot end a sequence by its limit.
+                ahead = session.submit() if all(states[i].steps + 1 < limits[i] for i in live) else None
+                chosen = session.read(ticket)
                 stats.decode_steps += 1
                 for i, token in zip(live, chosen):
                     states[i].accept(token)
+                if ahead is not None and any(states[i].finished for i in live):
+                    # A stop token ended a sequence, and the step ahead has run for every row
+                    # already: the other sequences keep its tokens, the ended one's is dropped.
+                    chosen = session.read(ahead)
+                    stats.decode_steps += 1
+                    for i, token in zip(live, chosen):
+                        if not states[i].finished:
+                            states[i].accept(token)
+                    ahead = None
                 if any(states[i].finished for i in live):
                     for i in [i for i in live if states[i].finished]:
                         finish(i)
                     live = [i for i in live if not states[i].finished]
-                    session = None
+                    session, ticket = None, None
+                else:
+                    ticket = ahead if ahead is not None else session.submit()
             stats.decode_ns += time.perf_counter_ns() - tick
         finally:
             for index in list(slots):

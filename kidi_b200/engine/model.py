@@ -98,6 +98,11 @@ class CausalLM:
     def cache_sources(self) -> List:
         return [entry.cache_from for entry in self.schedule]
 
+    def launch_signature(self, rows: int, longest: int) -> tuple:
+        """The launch choices of every layer for a decode step of `rows` sequences of at most
+        `longest` tokens: a captured step may be replayed while this stays the same."""
+        return tuple(layer.launch_signature(rows, longest) for layer in self.layers)
+
     # ------------------------------------------------------------------ forward
     def forward(self, ctx) -> torch.Tensor:
         """Runs the rows of `ctx` and returns float32 logits [wanted rows, vocab]."""

@@ -20,7 +20,6 @@ from . import ops
 from .ops import CacheGeometry, _check, c_float, c_int, c_longlong, c_void_p, cache_geometry
 
 FORCE_GENERIC = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1"
-FUSED_MERGE = os.environ.get("KIDI_B200_FUSED_MERGE", "1") == "1"
 # One token per sequence: the decode kernel normalises and rotates q and the new key itself and
 # writes the new key and value to the cache (one kernel less per layer); 0 switches that off.
 FUSE_ROTATION = os.environ.get("KIDI_B200_FUSE_ROTATION", "1") == "1"
@@ -232,13 +231,15 @@ def fuses_rotation(plan, qkv: torch.Tensor, *, heads: int, kv_heads: int, head_d
 
 
 def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step, rotation=None,
-        step_rows_cached: bool = False) -> None:
-    """`keys_in_step`: the step's own keys and values are read from qkv (else from the
+        step_rows_cached: bool = False, splits: Optional[int] = None, ring: Optional[bool] = None) -> None:
+    """`ctx` gives the step's `plan`, its device `tables` and `workspace(name, count, zero)`.
+    `keys_in_step`: the step's own keys and values are read from qkv (else from the
     cache, like the earlier ones). `step_rows_cached`: they are in the cache as well (a cache
     that keeps every page is written before attention), so a kernel may read everything
     from there. `rotation` (only where `fuses_rotation` said yes): dict(q_norm, k_norm, eps,
     cos, sin, rotary_dim, store): the kernel normalises and rotates q and the step's key
-    and, with `store`, writes the step's key and value to the cache."""
+    and, with `store`, writes the step's key and value to the cache. `splits` and `ring`
+    override the launcher's own choice of the decode kernel's form (tests of each form)."""
     plan, tables = ctx.plan, ctx.tables
     decode = plan.is_decode and not keys_in_step
     if not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode) or (kv_view is not None and kv_view.page_size != 64):
@@ -269,50 +270,78 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
         int(window or 0), float(scale), 0, 0, 1, 0)
     lib = library(head_dim)
     stream = ops._stream()
-    if decode:
-        longest = min(plan.max_total, int(window)) + 64 if window else plan.max_total
-        splits = getattr(ctx, "decode_splits", None) or decode_splits(qkv.shape[0], kv_heads, longest, qkv.device,
-                                                                       head_dim)
-        # One wave of blocks and few splits: the blocks of a (row, key/value head) form a
-        # thread-block cluster and merge through distributed shared memory (measured 13.5
-        # against 17.1 us a layer at batch 8). Clusters that must wait for several free slots of
-        # one GPC at once lose that again when the grid takes more than a wave (70.6 against
-        # 67.0 us at batch 64).
-        ring = getattr(ctx, "decode_ring", None)           # a test may ask for either form
-        if ring is None:
-            ring = splits == 1 and decode_ring(qkv.shape[0], kv_heads, qkv.device, head_dim)
-        ring = bool(ring) and ring_available(head_dim)
-        if _ring_set.get(head_dim) != ring:                # the form is a switch of the library, not of a launch
-            lib.kidi_attention_decode_ring(1 if ring else 0)
-            _ring_set[head_dim] = ring
-        one_wave = qkv.shape[0] * kv_heads * splits <= blocks_per_sm(head_dim, ring) * sm_count(qkv.device)
-        clustered = 1 < splits <= CLUSTER_SPLITS and heads // kv_heads <= 8 and one_wave
-        if splits > 1 and not clustered:
-            workspace = ctx.workspace("attention_partial", qkv.shape[0] * heads * splits * (head_dim + 2))
-            args.partial_out = workspace.data_ptr()
-            args.partial_stat = workspace.data_ptr() + qkv.shape[0] * heads * splits * head_dim * 4
-            # One wave of blocks: the last block of each (row, key/value head) merges its splits
-            # at the kernel's tail. More waves: a second kernel merges (the fence and the counter
-            # would hold up every block's slot; measured 6.55 against 6.39 ms per step at batch 64).
-            if heads // kv_heads <= 8 and splits <= 32 and FUSED_MERGE and one_wave:
-                # Zeroed when it is made; the kernel leaves every counter at zero.
-                args.counters = ctx.workspace("attention_counters", qkv.shape[0] * kv_heads, zero=True).data_ptr()
-        args.splits = splits
-        args.cache_rows = kv_view.keys.numel() // head_dim if kv_view.keys.is_contiguous() else 0
-        if rotation is not None:
-            item = qkv.element_size()
-            args.k_step = qkv.data_ptr() + heads * head_dim * item
-            args.v_step = qkv.data_ptr() + (heads + kv_heads) * head_dim * item
-            args.fuse = 1 | (2 if rotation.get("store", True) else 0)
-            q_norm, k_norm, cos, sin = (rotation.get(name) for name in ("q_norm", "k_norm", "cos", "sin"))
-            if q_norm is not None:
-                args.q_norm, args.k_norm = q_norm.data_ptr(), k_norm.data_ptr()
-                args.norm_is_float = int(q_norm.dtype == torch.float32)
-            if cos is not None:
-                args.cos_table, args.sin_table = cos.data_ptr(), sin.data_ptr()
-                args.rotary_dim = int(rotation["rotary_dim"])
-            args.eps = float(rotation.get("eps", 0.0))
-        _check(lib.kidi_attention_decode(ctypes.byref(args), stream), "attention_decode",
-               2 if splits > 1 and not clustered and not args.counters else 1)
-    else:
-        _check(lib.kidi_attention_prefill(ctypes.byref(args), plan.max_new, stream), "attention_prefill")
+    if not decode:
+        _check(lib.kidi_attention_prefill(ctypes.byref(args), plan.max_new, stream), "attention_prefill[mma.sync]")
+        return
+    rows = qkv.shape[0]
+    splits, ring = decode_form(rows, kv_heads, head_dim, plan.max_total, window, qkv.device, splits, ring)
+    if _ring_set.get(head_dim) != ring:                # the form is a switch of the library, not of a launch
+        lib.kidi_attention_decode_ring(1 if ring else 0)
+        _ring_set[head_dim] = ring
+    # One wave of blocks and few splits: the blocks of a (row, key/value head) form a thread-block
+    # cluster and merge through distributed shared memory. Clusters that must wait for several
+    # free slots of one GPC at once lose that again when the grid takes more than a wave.
+    one_wave = rows * kv_heads * splits <= blocks_per_sm(head_dim, ring) * sm_count(qkv.device)
+    clustered = 1 < splits <= CLUSTER_SPLITS and heads // kv_heads <= 8 and one_wave
+    form = "ring" if ring else "one block" if splits == 1 else "cluster" if clustered else "combine kernel"
+    if splits > 1 and not clustered:
+        workspace = ctx.workspace("attention_partial", rows * heads * splits * (head_dim + 2))
+        args.partial_out = workspace.data_ptr()
+        args.partial_stat = workspace.data_ptr() + rows * heads * splits * head_dim * 4
+        # One wave of blocks: the last block of each (row, key/value head) merges its splits at
+        # the kernel's tail. More waves: a second kernel merges (the fence and the counter would
+        # hold up every block's slot).
+        if heads // kv_heads <= 8 and splits <= 32 and one_wave:
+            # Zeroed when it is made; the kernel leaves every counter at zero.
+            args.counters = ctx.workspace("attention_counters", rows * kv_heads, zero=True).data_ptr()
+            form = "merge in the last block"
+    args.splits = splits
+    args.cache_rows = kv_view.keys.numel() // head_dim if kv_view.keys.is_contiguous() else 0
+    if rotation is not None:
+        args.k_step = qkv.data_ptr() + heads * head_dim * item
+        args.v_step = qkv.data_ptr() + (heads + kv_heads) * head_dim * item
+        args.fuse = 1 | (2 if rotation.get("store", True) else 0)
+        q_norm, k_norm, cos, sin = (rotation.get(name) for name in ("q_norm", "k_norm", "cos", "sin"))
+        if q_norm is not None:
+            args.q_norm, args.k_norm = q_norm.data_ptr(), k_norm.data_ptr()
+            args.norm_is_float = int(q_norm.dtype == torch.float32)
+        if cos is not None:
+            args.cos_table, args.sin_table = cos.data_ptr(), sin.data_ptr()
+            args.rotary_dim = int(rotation["rotary_dim"])
+        args.eps = float(rotation.get("eps", 0.0))
+    _check(lib.kidi_attention_decode(ctypes.byref(args), stream), f"attention_decode[{form}]",
+           2 if form == "combine kernel" else 1)
+
+
+def decode_form(rows: int, kv_heads: int, head_dim: int, longest: int, window, device: torch.device,
+                splits: Optional[int] = None, ring: Optional[bool] = None):
+    """(key splits, ring form) of decode attention for `rows` sequences of at most `longest`
+    tokens; `splits` / `ring`, when given, replace the policy's choice."""
+    reach = min(longest, int(window)) + 64 if window else longest
+    if splits is None:
+        splits = decode_splits(rows, kv_heads, reach, device, head_dim)
+    if ring is None:
+        ring = splits == 1 and decode_ring(rows, kv_heads, device, head_dim)
+    return splits, bool(ring) and ring_available(head_dim)
+
+
+class AttentionLauncher:
+    """What an attention part owns of the kernels: its geometry, the choice of kernel for a step
+    and the launch. Each part (hence each group of layers with a geometry of its own) chooses the
+    form of its decode kernel itself, from the rows of the step and the longest sequence."""
+
+    def __init__(self, *, heads: int, kv_heads: int, head_dim: int, scale: float, window=None):
+        self.geometry = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim)
+        self.scale, self.window = scale, window
+
+    def fuses_rotation(self, plan, qkv, **arguments) -> bool:
+        """Whether `run` can do norm, rotation and the cache write of this step itself."""
+        return fuses_rotation(plan, qkv, **self.geometry, **arguments)
+
+    def run(self, ctx, qkv, out, **arguments) -> None:
+        run(ctx, qkv, out, scale=self.scale, window=self.window, **self.geometry, **arguments)
+
+    def launch_signature(self, rows: int, longest: int, device: torch.device) -> tuple:
+        """What a captured decode step freezes of this launcher's choices."""
+        geometry = self.geometry
+        return decode_form(rows, geometry["kv_heads"], geometry["head_dim"], longest, self.window, device)

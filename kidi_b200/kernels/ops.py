@@ -100,7 +100,8 @@ def core():
                                          c_int, c_int, c_float, c_int, c_void_p]
         lib.kidi_silu_gate.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.kidi_gemm_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                                       c_longlong, c_longlong, c_longlong, c_void_p]
+                                       c_longlong, c_longlong, c_longlong, c_void_p, c_void_p]
+        lib.kidi_add_bias.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p]
         lib.kidi_rope_store.argtypes = [c_void_p, c_int, c_int, c_void_p]
         lib.kidi_attention_generic.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_argmax.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
@@ -110,7 +111,8 @@ def core():
         lib.kidi_argmax_slices.restype = c_int
         lib.kidi_advance_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_void_p]
-        for name in ("kidi_embedding", "kidi_add_rmsnorm", "kidi_silu_gate", "kidi_gemm_simt", "kidi_rope_store",
+        for name in ("kidi_embedding", "kidi_add_rmsnorm", "kidi_silu_gate", "kidi_gemm_simt", "kidi_add_bias",
+                     "kidi_rope_store",
                      "kidi_attention_generic", "kidi_argmax", "kidi_sample", "kidi_advance_decode"):
             getattr(lib, name).restype = c_int
         configure_library(lib)
@@ -217,10 +219,27 @@ def silu_gate(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torc
     return out
 
 
+def check_bias(bias: Optional[torch.Tensor], features: int) -> None:
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (features,) or not bias.is_contiguous()):
+        raise invalid_argument(f"a bias is a contiguous float32 vector of {features} elements")
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """y[r, :] += bias, in place (after a product the vendor library computed)."""
+    _need_cuda(y, bias)
+    if y.dim() != 2 or y.stride(1) != 1:
+        raise invalid_argument("add_bias takes a matrix with contiguous rows")
+    check_bias(bias, y.shape[1])
+    _check(core().kidi_add_bias(_ptr(y), dtype_code(y.dtype), _ptr(bias), y.shape[0], y.shape[1], y.stride(0),
+                                _stream()), "add_bias")
+    return y
+
+
 def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x @ weight.T with 32-bit fused multiply-adds in ascending k."""
-    _need_cuda(x, weight)
+              out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ weight.T (+ bias) with 32-bit fused multiply-adds in ascending k."""
+    _need_cuda(x, weight, bias)
+    check_bias(bias, weight.shape[0])
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
         raise invalid_argument(f"gemm: x {tuple(x.shape)} does not fit weight {tuple(weight.shape)}")
     if x.stride(1) != 1 or weight.stride(1) != 1:
@@ -231,7 +250,7 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     _check(core().kidi_gemm_simt(_ptr(x), dtype_code(x.dtype), _ptr(weight), dtype_code(weight.dtype), _ptr(out),
                                  dtype_code(out.dtype), M, N, K, x.stride(0), weight.stride(0), out.stride(0),
-                                 _stream()), "gemm_simt")
+                                 _ptr(bias), _stream()), "gemm_simt")
     return out
 
 

@@ -26,7 +26,7 @@ def _library():
     lib = ops.core()
     if not _bound:
         lib.kidi_gemm_skinny.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
-                                         c_longlong, c_longlong, c_int, c_int, c_void_p]
+                                         c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p]
         lib.kidi_gemm_skinny.restype = c_int
         _bound = True
     return lib
@@ -59,9 +59,10 @@ def _row_tiles(features: int) -> int:
 
 
 def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
-         row_tiles: Optional[int] = None) -> torch.Tensor:
-    """y = x @ weight.T for x [M <= 64, K], weight [N, K], both bfloat16."""
-    _need_cuda(x, weight)
+         row_tiles: Optional[int] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ weight.T (+ bias, float32) for x [M <= 64, K], weight [N, K], both bfloat16."""
+    _need_cuda(x, weight, bias)
+    ops.check_bias(bias, weight.shape[0])
     if not supports(x, weight) or x.shape[1] != weight.shape[1]:
         raise invalid_argument("gemm_skinny: the operands do not fit this kernel")
     M, K = x.shape
@@ -69,7 +70,8 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Opt
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     _check(_library().kidi_gemm_skinny(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0),
-                                       weight.stride(0), out.stride(0), 0, row_tiles or _row_tiles(N), _stream()),
+                                       weight.stride(0), out.stride(0), 0, row_tiles or _row_tiles(N), _ptr(bias),
+                                       _stream()),
            "gemm_skinny")
     return out
 
@@ -85,6 +87,6 @@ def gemm_silu_gate(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Te
     if out is None:
         out = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
     _check(_library().kidi_gemm_skinny(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), M, inter, K,
-                                       x.stride(0), weight.stride(0), out.stride(0), 1, row_tiles, _stream()),
+                                       x.stride(0), weight.stride(0), out.stride(0), 1, row_tiles, None, _stream()),
            "gemm_silu_gate[skinny]")
     return out

@@ -44,7 +44,7 @@ def _library():
     if not _bound:
         lib.kidi_gemm_tcgen05.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
                                           c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                          c_void_p]
+                                          c_void_p, c_void_p]
         lib.kidi_gemm_tcgen05.restype = c_int
         lib.kidi_gemm_tcgen05_token_tile.argtypes = [c_int]
         lib.kidi_gemm_tcgen05_token_tile.restype = c_int
@@ -97,26 +97,29 @@ def choose_splits(rows: int, features: int, K: int, gated: bool, device: torch.d
     return splits
 
 
-def _run(x, weight, out, features: int, gated: bool, splits: Optional[int]) -> None:
-    _need_cuda(x, weight, out)
+def _run(x, weight, out, features: int, gated: bool, splits: Optional[int], bias=None) -> None:
+    _need_cuda(x, weight, out, bias)
+    ops.check_bias(bias, features)
     rows, K = x.shape
     if splits is None:
         splits = choose_splits(rows, features, K, gated, x.device)
     workspace, counters, error = _device_state(x.device)
     _check(_library().kidi_gemm_tcgen05(
         _ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), rows, features, K, x.stride(0), weight.stride(0),
-        out.stride(0), 1 if gated else 0, splits, _ptr(workspace), _ptr(counters), _ptr(error), _stream()),
+        out.stride(0), 1 if gated else 0, splits, _ptr(workspace), _ptr(counters), _ptr(error), _ptr(bias),
+        _stream()),
         "gemm_silu_gate[tcgen05]" if gated else "gemm_tcgen05")
 
 
 def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
-         splits: Optional[int] = None) -> torch.Tensor:
-    """y = x @ weight.T for bfloat16 x [rows, K] and weight [features, K]; y bfloat16 or float32."""
+         splits: Optional[int] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ weight.T (+ bias, float32) for bfloat16 x [rows, K] and weight [features, K]; y bfloat16 or
+    float32."""
     if not supports(x, weight) or x.shape[1] != weight.shape[1]:
         raise invalid_argument("gemm_tcgen05: the operands do not fit this kernel")
     if out is None:
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
-    _run(x, weight, out, weight.shape[0], False, splits)
+    _run(x, weight, out, weight.shape[0], False, splits, bias)
     return out
 
 

@@ -10,7 +10,9 @@ u > p - W.
 
 Parameters (`spec.params`): hidden_size, num_heads, num_kv_heads, head_dim, qk_norm
 (bool), qk_norm_eps, position (name of a rotary encoding in `env.positions`, or None),
-window (tokens, or None), scale (None: 1/sqrt(head_dim)).
+window (tokens, or None), scale (None: 1/sqrt(head_dim)), qkv_bias and out_bias (bool,
+default false: the reference's Qwen3 projections carry none, src/kidi/layers/qwen3.cpp:14-15;
+its Linear has the option, src/kidi/layers/linear.cpp:181-190).
 """
 from __future__ import annotations
 
@@ -22,6 +24,7 @@ import torch
 from ..cache.sequence_cache import KVRequest
 from ..errors import invalid_argument, unsupported
 from ..kernels import ops
+from ..kernels.attention import AttentionLauncher
 from .base import Part
 from .linear import Linear
 from .registry import register_part
@@ -37,6 +40,8 @@ class Attention(Part):
         self.kv_heads = int(spec.param("num_kv_heads"))
         self.head_dim = int(spec.param("head_dim"))
         self.qk_norm = bool(spec.param("qk_norm", False))
+        self.qkv_bias = bool(spec.param("qkv_bias", False))
+        self.out_bias = bool(spec.param("out_bias", False))
         self.eps = float(spec.param("qk_norm_eps", 1e-6))
         self.window = spec.param("window", None)
         scale = spec.param("scale", None)
@@ -56,6 +61,8 @@ class Attention(Part):
         self.qkv: Optional[Linear] = None
         self.out: Optional[Linear] = None
         self.q_norm = self.k_norm = None
+        self.launcher = AttentionLauncher(heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
+                                          scale=self.scale, window=self.window)
 
     def parameter_specs(self) -> List[ParamSpec]:
         specs = [
@@ -65,14 +72,19 @@ class Attention(Part):
                 ("v_proj.weight", (self.kv_width, self.hidden)))),
             ParamSpec("o_proj.weight", (self.hidden, self.q_width)),
         ]
+        if self.qkv_bias:
+            specs.append(ParamSpec("qkv_proj.bias", (self.q_width + 2 * self.kv_width,), sources=(
+                ("q_proj.bias", (self.q_width,)), ("k_proj.bias", (self.kv_width,)), ("v_proj.bias", (self.kv_width,)))))
+        if self.out_bias:
+            specs.append(ParamSpec("o_proj.bias", (self.hidden,)))
         if self.qk_norm:
             specs.append(ParamSpec("q_norm.weight", (self.head_dim,), init=("one_plus_normal", 0.1)))
             specs.append(ParamSpec("k_norm.weight", (self.head_dim,), init=("one_plus_normal", 0.1)))
         return specs
 
     def bind(self, tensors) -> None:
-        self.qkv = Linear(tensors["qkv_proj.weight"])
-        self.out = Linear(tensors["o_proj.weight"])
+        self.qkv = Linear(tensors["qkv_proj.weight"], tensors.get("qkv_proj.bias"))
+        self.out = Linear(tensors["o_proj.weight"], tensors.get("o_proj.bias"))
         if self.qk_norm:
             self.q_norm, self.k_norm = tensors["q_norm.weight"], tensors["k_norm.weight"]
             if self.q_norm.dtype != self.k_norm.dtype:
@@ -80,6 +92,11 @@ class Attention(Part):
 
     def cache_requests(self) -> list:
         return [KVRequest(self.kv_heads, self.head_dim, int(self.window) if self.window is not None else None)]
+
+    def launch_signature(self, rows: int, longest: int) -> tuple:
+        """The choices a captured decode step of `rows` sequences of at most `longest` tokens
+        freezes for this part (the form of its decode kernel)."""
+        return self.launcher.launch_signature(rows, longest, self.env.device)
 
     def forward(self, x: torch.Tensor, ctx, views, owns_cache: bool) -> torch.Tensor:
         view = views[0]
@@ -98,17 +115,16 @@ class Attention(Part):
             raise unsupported("a layer that reads another layer's windowed cache takes one token per step")
         # One token per sequence on the tensor-core path: the attention kernel takes the rows as
         # the projection left them and does norm, rotation and the cache write itself.
-        fused = owns_cache and store_first and ctx.fuses_rotation(qkv, kv_view=view, q_norm=self.q_norm,
-                                                                  k_norm=self.k_norm, **rotate, **common)
+        fused = owns_cache and store_first and self.launcher.fuses_rotation(plan, qkv, kv_view=view, q_norm=self.q_norm,
+                                                                            k_norm=self.k_norm, **rotate)
         if not fused:
             ops.rope_store(qkv, q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, tables=ctx.tables, kv_view=view,
                            store=store_first, **rotate, **common)
         attended = torch.empty((qkv.shape[0], self.q_width), dtype=qkv.dtype, device=qkv.device)
         keys_in_step = owns_cache and not plan.is_decode
         rotation = dict(q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, store=True, **rotate) if fused else None
-        ctx.attention(qkv, attended, scale=self.scale, window=self.window, kv_view=view,
-                      keys_in_step=keys_in_step, rotation=rotation, step_rows_cached=store_first and not fused,
-                      **common)
+        self.launcher.run(ctx, qkv, attended, kv_view=view, keys_in_step=keys_in_step, rotation=rotation,
+                          step_rows_cached=store_first and not fused)
         if owns_cache and not store_first:
             ops.rope_store(qkv, q_norm=None, k_norm=None, eps=self.eps, tables=ctx.tables, kv_view=view, store=True,
                            transform=False, cos=None, sin=None, rotary_dim=0, **common)

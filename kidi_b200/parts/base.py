@@ -68,6 +68,14 @@ class Part:
     def cache_requests(self) -> list:
         return []
 
+    # --- captured steps
+    def launch_signature(self, rows: int, longest: int) -> tuple:
+        """What a captured decode step of `rows` sequences of at most `longest` tokens would
+        freeze of this part's launch choices (grid shapes that depend on the sequence length,
+        say). Two steps with equal signatures can replay one captured graph. Default: the
+        signatures of the part's children."""
+        return tuple(child.launch_signature(rows, longest) for child in self.children())
+
 
 def all_parameters(part: Part) -> List[Tuple[str, ParamSpec]]:
     """(prefix, spec) of the part and of its children, depth first."""

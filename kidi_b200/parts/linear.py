@@ -1,8 +1,10 @@
-"""y = x W^T for a weight stored [out, in], without bias.
+"""y = x W^T (+ b) for a weight stored [out, in] and an optional bias [out].
 
-This is the reference's Linear with `transpose=true, bias=false`
+This is the reference's Linear with `transpose=true` and its optional bias
 (src/kidi/layers/linear.cpp:98-101,181-190). It is a helper that parts own, not a
-registered part. Which kernel runs follows the element types:
+registered part. The bias is kept in 32-bit and added in the epilogue of this package's
+product kernels (after the vendor library's product, by a kernel of its own). Which
+kernel runs follows the element types:
 
 * a 32-bit input or a 32-bit weight: the 32-bit CUDA-core product (ascending-k fused
   multiply-adds; no reduced-precision matrix mode);
@@ -27,28 +29,34 @@ from ..kernels import ops
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
         if weight.dim() != 2:
             raise ValueError("a linear weight is a matrix [out, in]")
         self.weight = weight
         self.out_features, self.in_features = weight.shape
+        if bias is not None and bias.shape != (self.out_features,):
+            raise ValueError("a linear bias has one element per output feature")
+        self.bias = bias.float().contiguous() if bias is not None else None
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         out_dtype = out_dtype or x.dtype
-        weight = self.weight
+        weight, bias = self.weight, self.bias
         if x.dtype == torch.float32 or weight.dtype == torch.float32:
-            return ops.gemm_simt(x, weight, out_dtype, out=out)
+            return ops.gemm_simt(x, weight, out_dtype, out=out, bias=bias)
         from ..kernels import skinny, tcgen05
         if skinny.fits(x, weight):
-            return skinny.gemm(x, weight, out_dtype, out=out)
+            return skinny.gemm(x, weight, out_dtype, out=out, bias=bias)
         if weight.shape[0] >= tcgen05.MIN_FEATURES and tcgen05.fits(x, weight):
-            return tcgen05.gemm(x, weight, out_dtype, out=out)
+            return tcgen05.gemm(x, weight, out_dtype, out=out, bias=bias)
         if weight.shape[1] % 8 or x.stride(0) % 8:  # the library wants 16-byte rows; keep odd widths exact
-            return ops.gemm_simt(x, weight, out_dtype, out=out)
+            return ops.gemm_simt(x, weight, out_dtype, out=out, bias=bias)
+        ops.note("library_mm")
         if out is not None:
-            return torch.mm(x, weight.t(), out_dtype=out_dtype, out=out) if out_dtype != x.dtype else \
+            result = torch.mm(x, weight.t(), out_dtype=out_dtype, out=out) if out_dtype != x.dtype else \
                 torch.mm(x, weight.t(), out=out)
-        if out_dtype != x.dtype:
-            return torch.mm(x, weight.t(), out_dtype=out_dtype)
-        return torch.mm(x, weight.t())
+        elif out_dtype != x.dtype:
+            result = torch.mm(x, weight.t(), out_dtype=out_dtype)
+        else:
+            result = torch.mm(x, weight.t())
+        return ops.add_bias(result, bias) if bias is not None else result

@@ -19,10 +19,11 @@ def model_folders(tmp_path_factory):
     once per session into a temporary folder."""
     import torch
     from kidi_b200 import write_random_model
-    from tiny_configs import ALL
+    from tiny_configs import ALL, sharpen_logits
 
     root = tmp_path_factory.mktemp("models")
     folders = {}
     for seed, (name, config) in enumerate(ALL.items()):
         folders[name] = write_random_model(config, str(root / name), seed=seed, dtype=torch.bfloat16)
+        sharpen_logits(folders[name])
     return folders

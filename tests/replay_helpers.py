@@ -118,10 +118,33 @@ def first_bad_position(found: np.ndarray, expected: np.ndarray, tolerance: float
     return (int(bad[0]), float(errors[bad[0]])) if bad.size else None
 
 
-def assert_matches(found: Dict[str, np.ndarray], expected: Dict[str, np.ndarray], tolerance: float, what: str):
+def rms_error(found: Dict[str, np.ndarray], expected: Dict[str, np.ndarray]) -> float:
+    """Root of the mean squared difference over every logit of every request, each request's
+    differences relative to the larger of 1 and its largest expected magnitude."""
+    total, count = 0.0, 0
+    for name, reference in expected.items():
+        scale = max(1.0, float(np.abs(reference).max()))
+        total += float((((found[name] - reference) / scale) ** 2).sum())
+        count += reference.size
+    return (total / max(count, 1)) ** 0.5
+
+
+def worst_error(found: Dict[str, np.ndarray], expected: Dict[str, np.ndarray]) -> float:
+    return max(relative_error(found[name], reference) for name, reference in expected.items())
+
+
+def assert_matches(found: Dict[str, np.ndarray], expected: Dict[str, np.ndarray], tolerance, what: str):
+    """`tolerance`: the largest relative difference allowed, or a pair of that and a bound on the
+    root mean square of all differences (a fault that moves many logits a little shows there)."""
+    rms_bound = None
+    if isinstance(tolerance, tuple):
+        tolerance, rms_bound = tolerance
     for name, reference in expected.items():
         assert found[name].shape == reference.shape, f"{what}: {name} has shape {found[name].shape}"
         assert np.isfinite(found[name]).all(), f"{what}: {name} holds a non-finite logit"
         bad = first_bad_position(found[name], reference, tolerance)
         assert bad is None, (f"{what}: request {name} (length {reference.shape[0]}) first differs at position "
                              f"{bad[0]} with relative error {bad[1]:.3e} > {tolerance:.1e}")
+    if rms_bound is not None:
+        rms = rms_error(found, expected)
+        assert rms <= rms_bound, f"{what}: root mean square error {rms:.3e} > {rms_bound:.1e}"

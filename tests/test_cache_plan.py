@@ -104,10 +104,14 @@ def test_random_traffic_loses_nothing():
 
 def test_fixed_size_state_is_zeroed_when_a_slot_is_handed_out():
     cache = make_cache(requests=[[KVRequest(1, 16), StateRequest((3, 4))], [StateRequest((3, 4))], []])
-    assert len(cache.state_groups) == 1 and cache.state_groups[0].storage.shape == (2, 16, 3, 4)
+    # 16 slots and, as the last row, the padding slot's (what padding sequences of a captured step carry).
+    assert len(cache.state_groups) == 1 and cache.state_groups[0].storage.shape == (2, 17, 3, 4)
+    assert cache.padding_slot == 16 and cache.kv_groups[0].table.shape[0] == 17
     slot = cache.acquire()
     kv_view, state = cache.views(0)
-    assert state.shape == (16, 3, 4) and cache.views(2) == []
+    assert state.shape == (17, 3, 4) and cache.views(2) == []
+    with pytest.raises(KidiError):
+        cache.release(cache.padding_slot)          # never handed out, so never given back
     state[slot].fill_(5.0)
     cache.views(1)[0][slot].fill_(7.0)
     cache.release(slot)
@@ -177,3 +181,32 @@ def test_plan_validation(batch, starts):
     with pytest.raises(KidiError) as caught:
         build_plan(batch, starts, vocab_size=20)
     assert caught.value.code == ErrorCode.INVALID_ARGUMENT
+
+
+def test_values_of_a_page_are_cleared_when_it_is_handed_out_again():
+    """What a sequence left in its pages must not reach the next one that gets them: rows past
+    the next sequence's end are read with their page. Fresh pages are zero from the start and
+    are not cleared again."""
+    import torch
+    from kidi_b200.cache.sequence_cache import KVRequest, SequenceCache
+    cache = SequenceCache([[KVRequest(2, 16)], [KVRequest(2, 16)]], max_tokens=256, max_positions=256,
+                          dtype=torch.float32, device=torch.device("cpu"), page_size=64)
+    group = cache.kv_groups[0]
+    first = cache.acquire()
+    cache.reserve([(first, 130)])                       # three pages
+    pages = list(group.pages[first])
+    assert len(pages) == 3 and float(group.values.abs().sum()) == 0.0
+    group.values[:, pages] = float("nan")
+    group.keys[:, pages] = float("nan")
+    cache.commit([(first, 130)])
+    cache.release(first)
+    second = cache.acquire()
+    cache.reserve([(second, 70)])                       # two of the used pages come back
+    again = group.pages[second]
+    assert set(again) <= set(pages)
+    assert torch.isfinite(group.values[:, again]).all() and float(group.values[:, again].abs().sum()) == 0.0
+    left = [page for page in pages if page not in again]
+    assert torch.isnan(group.values[:, left]).all()     # a page nobody holds is not touched
+    cache.reserve([(second, 256)])                      # the third used page and a fresh one
+    assert torch.isfinite(group.values[:, group.pages[second]]).all()
+    cache.check()

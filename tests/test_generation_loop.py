@@ -19,6 +19,7 @@ class FakeBackend:
         self.log = []
         self.peak_live = 0
         self.acquired = []
+        self.read_upto = {}
 
     def acquire(self):
         slot = self.free.pop()
@@ -46,16 +47,26 @@ class FakeBackend:
         self.log.append(("open", len(slots)))
 
         class Session:
+            """Steps run when they are submitted (as on a device); a step is fed with the
+            tokens of the step before it."""
+
             def __init__(self):
                 self.tokens = list(tokens)
+                self.results = []
 
-            def step(self, fed=None):
-                assert fed is None or list(fed) == self.tokens   # the loop feeds back what it was given
+            def submit(self):
                 for slot, token in zip(slots, self.tokens):
+                    assert slot in backend.sequences, "a step ran for a sequence whose slot was given back"
                     backend.sequences[slot].append(token)
                 self.tokens = [backend._next(slot) for slot in slots]
                 backend.log.append(("decode", len(slots)))
-                return list(self.tokens)
+                self.results.append(list(self.tokens))
+                assert len(self.results) - backend.read_upto.get(id(self), 0) <= 2, "more than one step ahead"
+                return len(self.results) - 1
+
+            def read(self, ticket):
+                backend.read_upto[id(self)] = max(backend.read_upto.get(id(self), 0), ticket + 1)
+                return list(self.results[ticket])
 
         return Session()
 
@@ -110,6 +121,71 @@ def test_unequal_prompts_stop_tokens_and_early_finish():
     assert not backend.sequences and sorted(backend.free) == list(range(8))
     assert stats.prompt_tokens == 13 and stats.generated_tokens == sum(len(r.token_ids) for r in results)
     assert stats.batches == 1
+
+
+def test_decoding_runs_one_step_ahead_and_a_stop_token_costs_nothing():
+    """The loop submits step n+1 before it reads step n. When a stop token ends a sequence in
+    step n, the step that ran ahead is kept for the others, and no step is submitted ahead
+    when a sequence is about to reach its limit (its slot's room ends there)."""
+    backend = FakeBackend()
+    prompts = [[1, 2, 3], [7], [4, 4, 4, 4, 4, 4, 4], [9, 9]]
+    stops = [12, 28]
+    results = generate(backend, prompts, GenerationOptions(max_new_tokens=6, max_active=4), stop_ids=stops)
+    for prompt, result in zip(prompts, results):
+        tokens, reason = expected(prompt, 6, stops)
+        assert result.token_ids == tokens and result.finish_reason == reason
+        assert result.decoder_steps == len(tokens) + (reason == "stop")
+    # A sequence never holds more tokens than its prompt and its limit allow (checked per step by
+    # the fake session: a step for a released slot fails), and with limits alone no step is wasted:
+    backend = FakeBackend()
+    stats = GenerationStats()
+    generate(backend, [[1], [2, 3]], GenerationOptions(max_new_tokens=5, ignore_eos=True), stats=stats)
+    assert stats.decode_steps == 4 and [e for e in backend.log if e[0] == "decode"] == [("decode", 2)] * 4
+
+
+def test_a_captured_step_is_kept_per_launch_signature(monkeypatch):
+    """The engine's backend keeps one captured decode session per (batch bucket, launch
+    signature): a later call whose longest sequence changes the model's launch choices gets a
+    capture of its own, an equal one replays the first, and the number kept is bounded."""
+    from kidi_b200.engine import decode_graph, generate as loop
+
+    made = []
+
+    class FakeSession:
+        def __init__(self, engine, capacity, sampler, longest):
+            self.capacity, self.longest = capacity, longest
+            made.append((capacity, longest))
+
+        def load(self, *arguments):
+            pass
+
+    class FakeModel:
+        def launch_signature(self, rows, longest):
+            return (rows, -(-longest // 1000))      # the choice changes every 1,000 tokens
+
+    class FakeEngine:
+        vocab_size = 10
+        model = FakeModel()
+
+        class spec:
+            max_positions = 100000
+
+        class cache:
+            max_tokens, page_size, n_slots = 1 << 20, 64, 64
+
+    monkeypatch.setattr(decode_graph, "DecodeSession", FakeSession)
+    backend = loop.EngineBackend(FakeEngine(), sampler=None)
+    open_for = lambda rows, longest: backend.open_decode(list(range(rows)), [0] * rows, [0.0] * rows, list(range(rows)),
+                                                         [1] * rows, longest)
+    short = open_for(3, 300)
+    assert open_for(4, 900) is short and made == [(4, 300)]          # same bucket, same choices
+    long = open_for(3, 5000)
+    assert long is not short and made[-1] == (4, 5000)               # other choices: a capture of its own
+    assert open_for(3, 400) is short
+    for longest in range(10000, 10000 + 1000 * loop.MAX_KEPT_SESSIONS, 1000):
+        open_for(3, longest)
+    assert len(backend._sessions) == loop.MAX_KEPT_SESSIONS
+    assert open_for(3, 300) is not short                             # the least recently used was dropped
 
 
 def test_batches_follow_one_another_and_reuse_slots():

@@ -19,16 +19,26 @@ def load(folder, dtype, **options):
     return Engine.load(folder, dtype=dtype, **options)
 
 
-def check_teacher_forced(config, tensors, prompt, tokens, slack, stops=()):
-    """Every generated token is, within `slack`, the plain model's best next token
-    given the tokens before it (whole sequences, no cache)."""
+def check_teacher_forced(config, tensors, prompt, tokens, error, stops=()):
+    """Every generated token is the plain model's best next token given the tokens before it
+    (whole sequences, no cache), unless the plain model's two best logits lie closer together
+    than `error` times the largest logit (the bound on the engine's bfloat16 difference): then
+    either of those near-best tokens may have been chosen."""
     if not tokens:
-        return
+        return 0
     logits = plain_model.forward(config, tensors, list(prompt) + list(tokens))[len(prompt) - 1:-1].float().numpy()
+    close_calls = 0
     for position, token in enumerate(tokens):
         row = logits[position]
-        assert row[token] >= row.max() - slack, (prompt, tokens, position)
+        best, second = np.sort(row)[-1], np.sort(row)[-2]
+        bound = error * max(1.0, float(np.abs(row).max()))
+        if best - second >= bound:
+            assert token == int(np.argmax(row)), (prompt, tokens, position, float(best - second), bound)
+        else:
+            close_calls += 1
+            assert row[token] >= best - bound, (prompt, tokens, position)
         assert token not in stops
+    return close_calls
 
 
 @pytest.mark.parametrize("use_graph", [True, False])
@@ -57,11 +67,15 @@ def test_greedy_generation_in_bfloat16(model_folders, name):
     engine = load(model_folders[name], "bfloat16", max_tokens=1024)
     found = engine.generate(prompts, max_new_tokens=12, ignore_eos=True)
     eager = engine.generate(prompts, max_new_tokens=12, ignore_eos=True, use_graph=False)
+    from test_gpu_replay import BF16_TOLERANCES
+    error = BF16_TOLERANCES[name][0]          # three times the measured bfloat16 difference
+    close_calls = 0
     for prompt, tokens in zip(prompts, found):
         assert len(tokens) == 12
-        check_teacher_forced(config, tensors, prompt, tokens, slack=0.05)
+        close_calls += check_teacher_forced(config, tensors, prompt, tokens, error)
     for prompt, tokens in zip(prompts, eager):
-        check_teacher_forced(config, tensors, prompt, tokens, slack=0.05)
+        check_teacher_forced(config, tensors, prompt, tokens, error)
+    assert close_calls <= len(prompts) * 12 // 4, "too many tokens are decided within the rounding error to test much"
 
 
 def test_stop_tokens_end_a_sequence_early(model_folders):

@@ -38,7 +38,7 @@ def test_embedding(table_dtype):
 
 
 # -------------------------------------------------------------------- rmsnorm
-@pytest.mark.parametrize("hidden", [40, 1000, 1024, 4096, 5120, 8192])
+@pytest.mark.parametrize("hidden", [40, 1000, 1024, 3072, 4096, 5120, 7168, 8192, 9216])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(hidden, dtype):
     from kidi_b200.kernels import ops
@@ -146,6 +146,34 @@ def test_gemm_tcgen05_silu_gate(rows, splits):
     up = x.double() @ w[inter:].double().T
     out = tcgen05.gemm_silu_gate(x.to(DEVICE), w.to(DEVICE), splits=splits)
     close(out, gate / (1 + torch.exp(-gate)) * up, 5e-3, "fused silu gate (tcgen05)")
+    assert tcgen05.error_code(torch.device(DEVICE)) == 0
+
+
+@pytest.mark.parametrize("rows,shape", [(1, (389, 96)), (8, (4096, 1024)), (13, (130, 200)), (300, (389, 96))])
+def test_products_with_a_bias(rows, shape):
+    """y = x W^T + b in every product kernel (the bias in 32-bit, added in the epilogue) and
+    after a product of the vendor library."""
+    from kidi_b200.kernels import ops, skinny, tcgen05
+    N, K = shape
+    generator = torch.Generator().manual_seed(rows + N)
+    x = torch.randn(rows, K, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=generator) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=generator) * 3
+    expected = x.double() @ w.double().T + bias.double()
+    device_x, device_w, device_bias = x.to(DEVICE), w.to(DEVICE), bias.to(DEVICE)
+    for out_dtype, tolerance in ((torch.float32, 2e-5), (torch.bfloat16, 5e-3)):
+        close(ops.gemm_simt(device_x, device_w, out_dtype, bias=device_bias), expected, tolerance, "gemm_simt + bias")
+        close(ops.gemm_simt(device_x.float(), device_w.float(), out_dtype, bias=device_bias), expected, tolerance,
+              "gemm_simt in 32-bit + bias")
+        if rows <= 64:
+            close(skinny.gemm(device_x, device_w, out_dtype, bias=device_bias), expected, tolerance, "gemm_skinny + bias")
+        close(tcgen05.gemm(device_x, device_w, out_dtype, bias=device_bias), expected, tolerance, "gemm_tcgen05 + bias")
+        close(tcgen05.gemm(device_x, device_w, out_dtype, bias=device_bias, splits=2), expected, tolerance,
+              "gemm_tcgen05 split + bias")
+        product = (x.double() @ w.double().T).to(out_dtype).to(DEVICE)
+        close(ops.add_bias(product, device_bias), expected, tolerance, "add_bias")
+    with pytest.raises(Exception):
+        ops.add_bias(product, device_bias[:-1])
     assert tcgen05.error_code(torch.device(DEVICE)) == 0
 
 
@@ -264,10 +292,8 @@ def reference_attention(q, keys, values, positions, window, scale):
 class FakeContext:
     """What the attention launcher needs of a step."""
 
-    def __init__(self, plan, tables, splits=None, ring=None):
+    def __init__(self, plan, tables):
         self.plan, self.tables = plan, tables
-        self.decode_splits = splits
-        self.decode_ring = ring           # None: the launcher's own choice of the decode kernel's form
         self._held = {}
 
     def workspace(self, name, count, zero=False):
@@ -283,7 +309,8 @@ def launch_attention(kind, plan, tables, qkv, out, splits=None, ring=None, **arg
     else:
         assert attention.fast_fits(qkv.dtype, arguments["heads"], arguments["kv_heads"], arguments["head_dim"],
                                    plan.is_decode and not arguments["keys_in_step"])
-        attention.run(FakeContext(plan, tables, splits, ring), qkv, out, **arguments)
+        # splits / ring None: the launcher's own choice of the decode kernel's form
+        attention.run(FakeContext(plan, tables), qkv, out, splits=splits, ring=ring, **arguments)
 
 
 @pytest.mark.parametrize("kind,dtype", [("generic", torch.float32), ("generic", torch.bfloat16),
@@ -540,8 +567,8 @@ def test_decode_with_the_rotation_inside(geometry, splits, norm_dtype):
             ops.rope_store(rows, q_norm=q_norm, k_norm=k_norm, eps=1e-6, cos=cos, sin=sin, rotary_dim=rotary_dim,
                            tables=tables, kv_view=view, store=True, **common)
             rotation = None
-        attention.run(FakeContext(plan, tables, splits, ring), rows, out, scale=scale, window=window, kv_view=view,
-                      keys_in_step=False, rotation=rotation, **common)
+        attention.run(FakeContext(plan, tables), rows, out, scale=scale, window=window, kv_view=view,
+                      keys_in_step=False, rotation=rotation, splits=splits, ring=ring, **common)
         torch.cuda.synchronize()
         results.append((out, view.keys.clone(), view.values.clone(), [view.group.pages[slot] for slot in slots]))
     plain_out, plain_keys, plain_values, plain_pages = results[0]

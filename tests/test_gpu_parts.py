@@ -163,6 +163,63 @@ def test_attention_part_prompt_then_tokens(dtype, window):
             close(out[index], expected[b][heads_first[b] + step], tolerance, f"sequence {b}, token {heads_first[b] + step}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_part_with_biases(dtype):
+    """The same mixer with a bias on the fused q/k/v projection (bound from q, k and v biases by
+    the loader's concatenation rule) and on the output projection: prompts of 5 and 150 rows
+    (the few-row and the many-row products), then single tokens."""
+    from kidi_b200.parts.base import all_parameters
+    from kidi_b200.parts.registry import build_part
+    from kidi_b200.parts.spec import PartSpec
+    from kidi_b200.weights.loader import TensorDict, bind_parameters
+    hidden, heads, kv_heads, width = 64, 4, 2, 32
+    rope = PartSpec("rotary", {"head_dim": width, "rotary_dim": width, "theta": 1e4, "max_positions": 512})
+    env = make_env(dtype, positions={"rope": rope})
+    part = build_part("mixer", PartSpec("attention", {
+        "hidden_size": hidden, "num_heads": heads, "num_kv_heads": kv_heads, "head_dim": width, "qk_norm": True,
+        "qk_norm_eps": 1e-6, "position": "rope", "window": None, "qkv_bias": True, "out_bias": True}, "attn."), env)
+    generator = torch.Generator().manual_seed(21)
+    draw = lambda *shape, scale=1.0: (torch.randn(*shape, generator=generator) * scale).to(dtype)
+    q_rows, kv_rows = heads * width, kv_heads * width
+    stored = {"attn.q_proj.weight": draw(q_rows, hidden, scale=0.15), "attn.k_proj.weight": draw(kv_rows, hidden, scale=0.15),
+              "attn.v_proj.weight": draw(kv_rows, hidden, scale=0.15), "attn.o_proj.weight": draw(hidden, q_rows, scale=0.15),
+              "attn.q_proj.bias": draw(q_rows), "attn.k_proj.bias": draw(kv_rows), "attn.v_proj.bias": draw(kv_rows),
+              "attn.o_proj.bias": draw(hidden), "attn.q_norm.weight": 1 + draw(width, scale=0.1),
+              "attn.k_norm.weight": 1 + draw(width, scale=0.1)}
+    bound = bind_parameters(all_parameters(part), TensorDict(stored), engine_dtype=dtype, device=DEVICE)
+    assert bound["attn.qkv_proj.bias"].shape == (q_rows + 2 * kv_rows,)
+    part.bind({name[len("attn."):]: tensor for name, tensor in bound.items()})
+
+    def plain(x):                                    # the plain layer's steps with the biases added
+        length = x.shape[0]
+        w = lambda name: stored["attn." + name].double()
+        cos, sin = plain_model.rotary_tables(length, width, 1e4)
+        q = (x @ w("q_proj.weight").T + w("q_proj.bias")).reshape(length, heads, width)
+        k = (x @ w("k_proj.weight").T + w("k_proj.bias")).reshape(length, kv_heads, width)
+        v = (x @ w("v_proj.weight").T + w("v_proj.bias")).reshape(length, kv_heads, width)
+        q = plain_model.norm_then_rotate(q, w("q_norm.weight"), 1e-6, cos, sin)
+        k = plain_model.norm_then_rotate(k, w("k_norm.weight"), 1e-6, cos, sin)
+        return plain_model.causal_attention(q, k, v) @ w("o_proj.weight").T + w("o_proj.bias")
+
+    lengths, heads_first = [160, 12], [150, 5]
+    x = [torch.randn(n, hidden, generator=generator).to(dtype) for n in lengths]
+    expected = [plain(sequence.double()) for sequence in x]
+    cache, slots = step_context(part.cache_requests(), [0, 0], None, dtype)
+    ctx, growth = run_step(cache, slots, [[0] * n for n in heads_first], dtype)
+    out = part.forward(torch.cat([x[0][:150], x[1][:5]]).to(DEVICE), ctx, cache.views(0), True)
+    cache.commit(growth)
+    tolerance = 5e-6 if dtype == torch.float32 else 2e-2
+    close(out[:150], expected[0][:150], tolerance, "prompt 0 with biases")
+    close(out[150:], expected[1][:5], tolerance, "prompt 1 with biases")
+    for step in range(7):
+        ctx, growth = run_step(cache, slots, [[0], [0]], dtype)
+        rows = torch.stack([x[b][heads_first[b] + step] for b in range(2)]).to(DEVICE)
+        out = part.forward(rows, ctx, cache.views(0), True)
+        cache.commit(growth)
+        for b in range(2):
+            close(out[b], expected[b][heads_first[b] + step], tolerance, f"sequence {b}, token {heads_first[b] + step}")
+
+
 # ------------------------------------------------- schedules: a layer twice, a shared cache
 def test_schedule_names_a_layer_twice_and_shares_a_cache(tmp_path):
     """The run order is data: [0, 1, 0] runs layer 0 twice (each run with a cache of its
