@@ -17,13 +17,15 @@
 // V, which accumulates in 32-bit. Formulas: src/kidi/layers/qwen3.cpp:53-54,
 // src/kidi/runtime/vulkan/attention.comp:32-101; causal rule
 // src/kidi/model/gemma4.cpp:736-740.
+#include <atomic>
+#include <cstddef>
+
 #include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
 #include "attention_no_alloc.h"
 
-KIDI_DEFINE_PDL_FLAG()
 
 #ifndef KIDI_HEAD_DIM
 #error "compile with -DKIDI_HEAD_DIM=<head width>"
@@ -258,7 +260,6 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(Args a) {
     bf16* q_tile = reinterpret_cast<bf16*>(raw);            // [64][PITCH]
     bf16* k_tiles = q_tile + TILE * PITCH;                  // [2][64][PITCH]
     bf16* v_tiles = k_tiles + 2 * TILE * PITCH;             // [2][64][PITCH]
-    pdl_prologue();
     const int seq = blockIdx.y, head = blockIdx.z;
     const int q0 = blockIdx.x * TILE;
     const int count = a.seq_len[seq];
@@ -384,8 +385,6 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
         prefetch_l2(a.k_cache + offset);
         prefetch_l2(a.v_cache + offset);
     }
-    pdl_wait();
-    pdl_launch_dependents();
     if (tiles > 0) {
         for (int chunk = threadIdx.x; chunk < 16 * CHUNKS; chunk += THREADS) {
             const int r = chunk / CHUNKS, c = chunk - r * CHUNKS;
@@ -632,7 +631,6 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
         if (SWIZZLED) return tile + (col >> 6) * (TILE * 64) + r * 64 + ((((col & 63) >> 3) ^ (r & 7)) << 3);
         return tile + r * PITCH + col;
     };
-    pdl_prologue();
     const int split = blockIdx.x, kv_head = blockIdx.y, row = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -1056,7 +1054,6 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
 
 // grid (heads, rows): merges the splits of one (row, head) in split order.
 __global__ void attention_combine_kernel(Args a) {
-    pdl_prologue();
     const int head = blockIdx.x, row = blockIdx.y;
     const long long where = ((long long)row * a.heads + head) * a.splits;
     float top = -INFINITY;
@@ -1143,12 +1140,12 @@ KIDI_API int kidi_attention_prefill(const Args* args, int max_new, cudaStream_t 
     if (a.cache.head_dim != D || a.heads % a.kv_heads || a.heads > 65535 || a.seqs > 65535 || !aligned(a) ||
         (a.cache.table && a.cache.page_shift != 6))
         return KIDI_REFUSED_SIZE;
-    static bool configured = false;
-    if (!configured) {
+    static std::atomic<bool> configured{false};      // setting the attribute twice is harmless
+    if (!configured.load(std::memory_order_acquire)) {
         cudaError_t status = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   (int)PREFILL_SHARED);
         if (status != cudaSuccess) return (int)status;
-        configured = true;
+        configured.store(true, std::memory_order_release);
     }
     dim3 grid((max_new + TILE - 1) / TILE, a.seqs, a.heads);
     return kidi_launch(attention_prefill_kernel, grid, THREADS, PREFILL_SHARED, stream, a);
@@ -1161,7 +1158,7 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
     if (a.rows <= 0) return 0;
     const int group = a.kv_heads > 0 ? a.heads / a.kv_heads : 0;
     if (a.cache.head_dim != D || a.heads % a.kv_heads || group > 16 || a.kv_heads > 65535 || a.rows > 65535 ||
-        !aligned(a) || a.cache.page_shift != 6 || a.splits < 1 || (a.counters && a.splits > 32))
+        !aligned(a) || a.cache.page_shift != 6 || a.splits < 1 || a.splits > 65535 || (a.counters && a.splits > 32))
         return KIDI_REFUSED_SIZE;
     if (a.fuse) {   // the rotation inside the kernel: the narrow kernel, vectors of eight elements
         if (group > 8 || !a.k_step || !a.v_step || (a.ldkv & 7) || (a.rotary_dim & 15) || a.rotary_dim > D ||
@@ -1183,8 +1180,8 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
         if (!status) status = page_map(&v_map, a.v_cache, a.cache_rows);
         if (status) return status;
     }
-    static bool configured = false;
-    if (!configured) {
+    static std::atomic<bool> configured{false};      // setting the attributes twice is harmless
+    if (!configured.load(std::memory_order_acquire)) {
         cudaError_t status = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   (int)DECODE_SHARED);
         const void* narrow[6] = {(const void*)attention_decode_narrow_kernel<false, 0>,
@@ -1197,7 +1194,7 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
         for (int i = 0; i < 6 && status == cudaSuccess; ++i)
             status = cudaFuncSetAttribute(narrow[i], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizes[i >> 1]);
         if (status != cudaSuccess) return (int)status;
-        configured = true;
+        configured.store(true, std::memory_order_release);
     }
     dim3 grid(a.splits, a.kv_heads, a.rows);
     const int form = !swizzled ? 0 : kidi_decode_ring ? 2 : 1;
@@ -1232,30 +1229,42 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
 // runtime for the device address once per device and passes that to the kernels.
 static __device__ __align__(256) float kidi_static_scratch[KIDI_STATIC_SCRATCH_FLOATS];
 
+// The published argument block is the kernels' own, field for field.
+static_assert(sizeof(KidiAttentionArgs) == sizeof(Args) && sizeof(KidiCacheGeometry) == sizeof(CacheGeometry) &&
+                  offsetof(KidiAttentionArgs, out) == offsetof(Args, out) &&
+                  offsetof(KidiAttentionArgs, splits) == offsetof(Args, splits) &&
+                  offsetof(KidiAttentionArgs, cache_rows) == offsetof(Args, cache_rows),
+              "attention_no_alloc.h and the kernels disagree about the argument block");
+
+// Floats of workspace a call needs; -1 when rows, heads or splits lie outside the bounds
+// (checked before the product is formed, so that it cannot overflow).
 KIDI_API long long kidi_attention_decode_static_need(int rows, int heads, int splits) {
+    if (rows < 0 || heads < 0 || splits < 1 || rows > KIDI_STATIC_MAX_ROWS || heads > KIDI_STATIC_MAX_HEADS ||
+        splits > KIDI_STATIC_MAX_SPLITS)
+        return -1;
     return splits > 1 ? (long long)rows * heads * splits * (D + 2) : 0;
 }
 
 KIDI_API int kidi_attention_decode_static(const KidiAttentionArgs* args, cudaStream_t stream) {
     constexpr int MAX_DEVICES = 64;
-    static float* scratch_of_device[MAX_DEVICES] = {nullptr};
+    static std::atomic<float*> scratch_of_device[MAX_DEVICES];      // zero-initialised
     Args a = *reinterpret_cast<const Args*>(args);
     if (a.rows <= 0) return 0;
-    if (a.splits < 1 || a.heads <= 0) return KIDI_REFUSED_SIZE;
     const long long need = kidi_attention_decode_static_need(a.rows, a.heads, a.splits);
+    if (need < 0 || a.heads <= 0) return KIDI_REFUSED_SIZE;
     if (need > KIDI_STATIC_SCRATCH_FLOATS) return KIDI_REFUSED_SIZE;  // more splits than the fixed workspace holds
     int device = -1;
     cudaError_t status = cudaGetDevice(&device);
     if (status != cudaSuccess) return (int)status;
     if (device < 0 || device >= MAX_DEVICES) return KIDI_REFUSED_SIZE;
-    if (!scratch_of_device[device]) {  // set-up, once per device, with that device current
-        float* address = nullptr;
-        status = cudaGetSymbolAddress((void**)&address, kidi_static_scratch);
+    float* scratch = scratch_of_device[device].load(std::memory_order_acquire);
+    if (!scratch) {  // set-up, once per device, with that device current (threads that race here find the same address)
+        status = cudaGetSymbolAddress((void**)&scratch, kidi_static_scratch);
         if (status != cudaSuccess) return (int)status;
-        scratch_of_device[device] = address;
+        scratch_of_device[device].store(scratch, std::memory_order_release);
     }
-    a.partial_out = scratch_of_device[device];
-    a.partial_stat = scratch_of_device[device] + (long long)a.rows * a.heads * a.splits * D;
+    a.partial_out = scratch;
+    a.partial_stat = scratch + (long long)a.rows * a.heads * a.splits * D;
     a.counters = nullptr;  // the splits are merged by the second kernel
     return kidi_attention_decode(&a, stream);
 }

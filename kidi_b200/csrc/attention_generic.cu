@@ -41,7 +41,6 @@ struct RopeStoreArgs {
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128) rope_store_kernel(RopeStoreArgs a) {
     __shared__ float normed[4][256];
-    pdl_prologue();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_heads = a.heads + 2 * a.kv_heads;
     const long long item = (long long)blockIdx.x * 4 + warp;
@@ -139,7 +138,6 @@ __device__ __forceinline__ void load8(const bf16* p, float (&w)[8]) {
 // Needs head_dim and rotary_dim/2 to be multiples of 8 and 16-byte aligned rows.
 template <typename TW>
 __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a, int group_lanes) {
-    pdl_prologue();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_heads = a.heads + 2 * a.kv_heads;
     const int per_warp = 32 / group_lanes;
@@ -287,7 +285,6 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(AttentionArgs a)
     __shared__ float query[256];
     __shared__ float part_acc[4][256];
     __shared__ float part_max[4], part_sum[4];
-    pdl_prologue();
     const int row = blockIdx.x, head = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d = a.head_dim;

@@ -36,7 +36,6 @@
 
 #include "common.cuh"
 
-KIDI_DEFINE_PDL_FLAG()
 
 #ifndef KIDI_HEAD_DIM
 #error "compile with -DKIDI_HEAD_DIM=64 or 128"

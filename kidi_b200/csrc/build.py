@@ -107,9 +107,6 @@ def library_flags(defines: Optional[Mapping[str, object]] = None) -> Sequence[st
     flags = list(ARCH_FLAGS) + list(COMMON_FLAGS) + ["-I", SOURCE_DIR]
     for key, value in sorted((defines or {}).items()):
         flags.append(f"-D{key}={value}")
-    # Experiments: KIDI_B200_EXTRA_DEFINES="NAME=VALUE,..." is added to every library.
-    for item in filter(None, os.environ.get("KIDI_B200_EXTRA_DEFINES", "").split(",")):
-        flags.append(f"-D{item}")
     return flags
 
 

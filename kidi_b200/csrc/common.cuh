@@ -76,73 +76,20 @@ __device__ __forceinline__ long long cache_row_offset(const CacheGeometry& g, in
 
 static inline int kidi_launch_status() { return (int)cudaGetLastError(); }
 
-// ---------------------------------------------------------------------------
-// Programmatic dependent launch (off unless kidi_set_pdl(1) is called; measured on
-// B200 inside a captured decode step it made the step slower, 5.9 ms against 4.2 ms, so
-// it is kept as an experiment switch only). With it, every kernel of this package is
-// launched with "programmatic stream serialization": it may become resident while the
-// kernel before it in the stream is still running, and it calls pdl_wait() before it
-// reads or writes anything an earlier kernel of the same step touches. What it does before
-// that (index arithmetic, reading weights and the step's integer tables, prefetching
-// weights into L2) overlaps the tail of its predecessor, which hides the launch
-// latency of the few hundred small kernels of a decode step. pdl_wait() returns when
-// the preceding kernel has completed and its writes are visible, so the chain of
-// kernels keeps the order of the stream. Memory that is only written between graph
-// launches (weights, block tables) or by the last kernel of the previous step
-// (positions) may be read before the wait.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
-// A kernel lets the next one start only once it runs itself (after its own wait): then at
-// most one kernel sits on the SMs waiting, in slots that the running kernel does not need.
-// (Letting dependents start before the wait makes a whole chain of future kernels resident
-// at once; they take the slots that the later waves of the running kernel need: measured
-// 5.5 against 3.9 ms per decode step. In this order the replayed decode graph still loses
-// 2% against ordinary launches, 3.75 against 3.66 ms, and 4% when only the weight-streaming
-// products start early, 3.80 against 3.65 ms, so the switch stays off.)
-__device__ __forceinline__ void pdl_prologue() {
-    pdl_wait();
-    pdl_launch_dependents();
-}
 __device__ __forceinline__ void prefetch_l2(const void* pointer) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(pointer));
-}
-
-extern int kidi_pdl_flag;  // one per library; 0 launches every kernel the ordinary way, bit 0 every
-                           // kernel as a dependent launch, bit 1 only the small ones (kidi_launch_small)
-
-#define KIDI_DEFINE_PDL_FLAG()                                              \
-    int kidi_pdl_flag = 0;                                                  \
-    KIDI_API void kidi_set_pdl(int enabled) { kidi_pdl_flag = enabled; }
-
-template <typename... Expected, typename... Actual>
-static inline int kidi_launch_as(bool dependent, void (*kernel)(Expected...), dim3 grid, dim3 block, size_t shared,
-                                 cudaStream_t stream, Actual&&... arguments) {
-    cudaLaunchConfig_t config = {};
-    config.gridDim = grid;
-    config.blockDim = block;
-    config.dynamicSmemBytes = shared;
-    config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute;
-    config.numAttrs = dependent ? 1 : 0;
-    cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<Expected>(arguments)...);
-    return status != cudaSuccess ? (int)status : (int)cudaGetLastError();
 }
 
 template <typename... Expected, typename... Actual>
 static inline int kidi_launch(void (*kernel)(Expected...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
                               Actual&&... arguments) {
-    return kidi_launch_as((kidi_pdl_flag & 1) != 0, kernel, grid, block, shared, stream, static_cast<Actual&&>(arguments)...);
-}
-
-// A kernel of a few small blocks between two large ones (a norm between two products): as a
-// dependent launch its blocks are resident, waiting, when the kernel before it ends.
-template <typename... Expected, typename... Actual>
-static inline int kidi_launch_small(void (*kernel)(Expected...), dim3 grid, dim3 block, size_t shared,
-                                    cudaStream_t stream, Actual&&... arguments) {
-    return kidi_launch_as((kidi_pdl_flag & 3) != 0, kernel, grid, block, shared, stream, static_cast<Actual&&>(arguments)...);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<Expected>(arguments)...);
+    return status != cudaSuccess ? (int)status : (int)cudaGetLastError();
 }
 
 // The same with the blocks along x grouped into thread-block clusters of `cluster_x`
@@ -155,15 +102,13 @@ static inline int kidi_launch_clusters(void (*kernel)(Expected...), dim3 grid, d
     config.blockDim = block;
     config.dynamicSmemBytes = shared;
     config.stream = stream;
-    cudaLaunchAttribute attribute[2];
+    cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeClusterDimension;
     attribute[0].val.clusterDim.x = cluster_x;
     attribute[0].val.clusterDim.y = 1;
     attribute[0].val.clusterDim.z = 1;
-    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = (kidi_pdl_flag & 1) ? 2 : 1;
+    config.numAttrs = 1;
     cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<Expected>(arguments)...);
     return status != cudaSuccess ? (int)status : (int)cudaGetLastError();
 }

@@ -8,7 +8,6 @@
 // 32-bit in every engine dtype, and the sum of squares and the inverse root are 32-bit.
 #include "common.cuh"
 
-KIDI_DEFINE_PDL_FLAG()
 
 // Four consecutive elements of a row as 32-bit values, whatever the stored type.
 __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -30,7 +29,6 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                  const int* __restrict__ tokens, int hidden, int vocab, float scale) {
-    pdl_prologue();
     const int row = blockIdx.x;
     const int token = tokens[row];
     float* destination = out + (long long)row * hidden;
@@ -74,7 +72,6 @@ add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, c
                    TY* __restrict__ y, const int* __restrict__ row_index, int hidden, float eps, int write_residual) {
     extern __shared__ float staged[];
     __shared__ float scratch[32];
-    pdl_prologue();
     const int r = blockIdx.x;
     const long long s = row_index ? row_index[r] : r;
     float* h = residual + s * hidden;
@@ -102,7 +99,6 @@ __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_vector_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const TW* __restrict__ weight,
                           TY* __restrict__ y, const int* __restrict__ row_index, float eps, int write_residual) {
     __shared__ float scratch[32];
-    pdl_prologue();
     constexpr int hidden = THREADS * 4 * CHUNKS;
     const int r = blockIdx.x;
     const long long s = row_index ? row_index[r] : r;
@@ -148,7 +144,7 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const void* we
                          !((uintptr_t)y & 15);
 #define KIDI_VECTOR_CASE(CHUNKS)                                                                              \
     if (vectors && hidden == THREADS * 4 * CHUNKS)                                                            \
-        return kidi_launch_small(add_rmsnorm_vector_kernel<TD, TW, TY, THREADS, CHUNKS>, rows, THREADS, 0, stream, \
+        return kidi_launch(add_rmsnorm_vector_kernel<TD, TW, TY, THREADS, CHUNKS>, rows, THREADS, 0, stream, \
                            residual, (const TD*)delta, (const TW*)weight, (TY*)y, row_index, eps, write_residual);
     KIDI_VECTOR_CASE(1)     // every multiple of 1024 up to 8192 elements
     KIDI_VECTOR_CASE(2)
@@ -166,7 +162,7 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const void* we
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (status != cudaSuccess) return (int)status;
     }
-    return kidi_launch_small(kernel, rows, THREADS, shared, stream, residual, (const TD*)delta, (const TW*)weight, (TY*)y,
+    return kidi_launch(kernel, rows, THREADS, shared, stream, residual, (const TD*)delta, (const TW*)weight, (TY*)y,
                        row_index, hidden, eps, write_residual);
 }
 
@@ -199,7 +195,6 @@ KIDI_API int kidi_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
 __global__ void advance_decode_kernel(int* __restrict__ tokens, const int* __restrict__ selected,
                                       const int* __restrict__ row_seq, int* __restrict__ row_pos,
                                       int* __restrict__ seq_start, int* __restrict__ steps, int rows, int vocab) {
-    pdl_prologue();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows || row_seq[r] < 0) return;
     const int token = selected[r];
@@ -220,7 +215,6 @@ KIDI_API int kidi_advance_decode(int* tokens, const int* selected, const int* ro
 // gate_up [rows, 2*inter] (gate = first inter columns, up = last inter) -> out [rows, inter]
 template <typename T>
 __global__ void silu_gate_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter) {
-    pdl_prologue();
     const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (index >= total) return;
     const long long row = index / inter;
@@ -233,7 +227,6 @@ __global__ void silu_gate_kernel(const T* __restrict__ gate_up, T* __restrict__ 
 // The same for bfloat16 rows whose width is a multiple of 8: eight elements (16 bytes) per thread.
 __global__ void silu_gate_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, long long groups,
                                         int inter) {
-    pdl_prologue();
     const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (index >= groups) return;
     const int per_row = inter >> 3;
@@ -278,7 +271,6 @@ KIDI_API int kidi_silu_gate(const void* gate_up, void* out, int dtype, int rows,
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, long long total, int features,
                                 long long ldy) {
-    pdl_prologue();
     const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (index >= total) return;
     const long long row = index / features;

@@ -19,7 +19,6 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restr
                  long long ldx, long long ldw, long long ldy, const float* __restrict__ bias) {
     __shared__ float xs[TILE_K][TILE + PAD];
     __shared__ float ws[TILE_K][TILE + PAD];
-    pdl_prologue();
     const int tx = threadIdx.x & 15;   // 4 output columns (n) each
     const int ty = threadIdx.x >> 4;   // 4 output rows (m) each
     const int m0 = blockIdx.y * TILE, n0 = blockIdx.x * TILE;

@@ -17,13 +17,6 @@
 // rows and the 16 matching up rows.
 #include "common.cuh"
 
-#ifndef KIDI_SKINNY_HOIST
-#define KIDI_SKINNY_HOIST 1
-#endif
-#ifndef KIDI_SKINNY_PREFETCH
-#define KIDI_SKINNY_PREFETCH 0  // measured on B200: asking a block's own rows into L2 just before loading them costs time
-#endif
-
 namespace {
 
 constexpr int WARPS = 8;
@@ -94,13 +87,6 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* _
 
     const int slices = (K + 31) >> 5;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    // The weights do not depend on the kernel before this one: the first slices are
-    // loaded, and the rest of this block's weight rows are asked into L2, before the
-    // wait for that kernel; only the batch operand has to wait.
-#if !KIDI_SKINNY_HOIST
-    pdl_wait();
-    pdl_launch_dependents();
-#endif
     uint4 a[UNROLL][MT][2], b[UNROLL][NT];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -112,25 +98,6 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* _
             for (int h = 0; h < 2; ++h)
                 a[u][mt][h] = (ok && weight_ok[mt][h]) ? load_streaming(weight_row[mt][h] + k) : zero;
     }
-#if KIDI_SKINNY_PREFETCH
-    {
-        // One 128-byte line per prefetch: thread i of the block takes lines i, i + 256, ...
-        const int lines_per_row = (K * 2 + 127) >> 7;
-        const int rows = MT * 16;
-        for (int line = threadIdx.x; line < rows * lines_per_row; line += WARPS * 32) {
-            const int r = line / lines_per_row, c = line - r * lines_per_row;
-            if (c * 64 < WARPS * UNROLL * 32 || (c + 1) * 64 > K) continue;  // on their way already, or a ragged end
-            const int mt = r >> 4, local = r & 15;
-            const int feature = n0 + (GATED ? 0 : mt * 16) + local;
-            if (feature < N)
-                prefetch_l2(w + ((GATED && mt == 1 ? (long long)N : 0) + feature) * ldw + c * 64);
-        }
-    }
-#endif
-#if KIDI_SKINNY_HOIST
-    pdl_wait();
-    pdl_launch_dependents();
-#endif
     for (int first = warp; first < slices; first += WARPS * UNROLL) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {

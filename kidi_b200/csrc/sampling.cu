@@ -54,7 +54,6 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
                                                          int vocab) {
     __shared__ Best scratch[THREADS / 32];
     __shared__ int invalid;
-    pdl_prologue();
     const Best best = block_argmax(logits + (long long)blockIdx.x * vocab, vocab, 1.f, scratch, &invalid);
     if (threadIdx.x == 0) out[blockIdx.x] = best.index;
 }
@@ -67,7 +66,6 @@ argmax_slices_kernel(const float* __restrict__ logits, float* __restrict__ slice
                      int vocab, int slices) {
     __shared__ Best scratch[THREADS / 32];
     __shared__ int invalid;
-    pdl_prologue();
     const int slice = blockIdx.x, row = blockIdx.y;
     const int width = (vocab + slices - 1) / slices;
     const int begin = min(vocab, slice * width), count = min(vocab, begin + width) - begin;
@@ -81,7 +79,6 @@ argmax_slices_kernel(const float* __restrict__ logits, float* __restrict__ slice
 
 __global__ void argmax_merge_kernel(const float* __restrict__ slice_value, const int* __restrict__ slice_index,
                                     int* __restrict__ out, int slices) {
-    pdl_prologue();
     const int row = blockIdx.x;
     if (threadIdx.x != 0) return;
     Best best{-INFINITY, -1};
@@ -112,7 +109,6 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
               unsigned long long seed, const long long* __restrict__ keys, const int* __restrict__ steps) {
     __shared__ float sums[THREADS];
     __shared__ float reduce[32];
-    pdl_prologue();
     const int r = blockIdx.x;
     const float* row = logits + (long long)r * vocab;
     // out[r] holds the row's argmax already (the two greedy stages ran before this kernel).

@@ -24,8 +24,8 @@ FORCE_GENERIC = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1"
 # writes the new key and value to the cache (one kernel less per layer); 0 switches that off.
 FUSE_ROTATION = os.environ.get("KIDI_B200_FUSE_ROTATION", "1") == "1"
 # Head widths that are multiples of 64: the decode kernel takes whole pages by TMA tensor copies
-# (0: row by row into padded tiles, as for the other widths).
-DECODE_SWIZZLED = os.environ.get("KIDI_B200_DECODE_SWIZZLED", "1") == "1"
+# (False, for tests of the other form at such a width: row by row into padded tiles).
+DECODE_SWIZZLED = True
 # The page-copying decode kernel keeps a ring of three tiles (keys and values in turn), so that
 # four blocks of head width 128 fit an SM (0: two key and two value tiles, three blocks).
 # "force": wherever the kernel has that form (for tests of it on small batches).
@@ -71,7 +71,6 @@ def library(head_dim: int) -> ctypes.CDLL:
         lib.kidi_attention_decode_ring.restype = None
         lib.kidi_attention_decode_ring(0)
         _ring_set[head_dim] = False
-        ops.configure_library(lib)
         _libraries[head_dim] = lib
     return lib
 
@@ -86,7 +85,6 @@ def tensor_memory_library(head_dim: int) -> ctypes.CDLL:
             c_float, c_void_p, c_void_p]
         lib.kidi_attention_prefill_tcgen05.restype = c_int
         lib.kidi_attention_tcgen05_timeout_flag.restype = c_int
-        ops.configure_library(lib)
         _tensor_memory_libraries[head_dim] = lib
     return lib
 
@@ -170,9 +168,7 @@ def blocks_per_sm(head_dim: int = 128, ring: bool = False) -> int:
 def decode_ring(rows: int, kv_heads: int, device: torch.device, head_dim: int) -> bool:
     """Whether decode attention takes its ring form: one block per (row, key/value head), no
     splits. The ring holds fewer bytes in flight per block and pays a second barrier per
-    tile (measured on a B200 at head width 128: 8.4 against 7.8 us a layer at batch 1, 28.6
-    against 26.1 at batch 32), so it is taken only where a fourth block per SM saves a round
-    of blocks: 46.6 against 53.5 us a layer at batch 64 and 1,060 tokens."""
+    tile, so it is taken only where one more block per SM saves a round of blocks."""
     if not ring_available(head_dim):
         return False
     if DECODE_RING_ALWAYS:

@@ -115,19 +115,8 @@ def core():
                      "kidi_rope_store",
                      "kidi_attention_generic", "kidi_argmax", "kidi_sample", "kidi_advance_decode"):
             getattr(lib, name).restype = c_int
-        configure_library(lib)
         _core = lib
     return _core
-
-
-def configure_library(lib) -> None:
-    """Settings every kernel library takes: KIDI_B200_PDL=1 launches every kernel with
-    programmatic dependent launch, KIDI_B200_PDL=norm only the norms between the products
-    (experiment switches; off by default)."""
-    import os
-    lib.kidi_set_pdl.argtypes = [c_int]
-    lib.kidi_set_pdl.restype = None
-    lib.kidi_set_pdl({"1": 1, "norm": 2}.get(os.environ.get("KIDI_B200_PDL", "0"), 0))
 
 
 # ----------------------------------------------------------------- structures

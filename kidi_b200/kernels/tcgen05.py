@@ -8,10 +8,8 @@ needs a workspace and counters that this module keeps per device (allocated once
 replaced, so that captured graphs can hold their addresses).
 
 KIDI_B200_TCGEN05_MAX_ROWS bounds the rows for which `fits` says yes (0 switches the
-kernel off); above it the caller uses the matrix library. The default is 16: measured on
-a B200 as whole decode steps of the 8B shape, runs interleaved, this kernel equals the
-library at 16 rows (4.041 ms either way) and loses to it above (4.484 against 4.428 ms at
-32 rows, 5.475 against 5.403 at 64).
+kernel off); above it the caller uses the matrix library, which streams weights faster
+from 17 rows on.
 """
 from __future__ import annotations
 
@@ -28,8 +26,7 @@ from .ops import _check, _need_cuda, _ptr, _stream, c_int, c_longlong, c_void_p,
 MAX_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_MAX_ROWS", "16"))
 MIN_FEATURES = 16384                    # the dispatcher uses this kernel for weights at least this tall
 MIN_GATED_ROWS = 9                      # and its fused SiLU gate from this many rows on (below: the skinny kernel)
-# The fused gate above this many rows (and within MAX_ROWS): at 64 rows the kernel without the
-# gate followed by the gate kernel is faster (5.475 against 5.504 ms a step).
+# The most rows for the fused gate (and within MAX_ROWS): beyond, the product followed by the gate kernel is faster.
 MAX_GATED_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_MAX_GATED_ROWS", "32"))
 WORKSPACE_FLOATS = 8 * 1024 * 1024      # 32 MiB of partial tiles
 COUNTERS = 16384

@@ -25,8 +25,11 @@ SHAPE = {
 SEQUENCES = 64
 DECODED = 3            # the last tokens of every sequence come one by one
 LONG = 200             # the first sequence is this long: several pages, so that its keys are split
+# Relative to a sequence's largest logit (about 6). Measured on a B200 over all batch sizes:
+# 6.4e-6 in 32-bit (products of 4096 to 12288 terms), 1.1e-2 to 1.3e-2 in bfloat16; the bounds
+# are three and two times that. Every case records what it measures (`record_property`).
 FP32_TOLERANCE = 2e-5
-BF16_TOLERANCE = 2.5e-2   # measured: see DESIGN.md (tests); relative to the largest logit (about 6)
+BF16_TOLERANCE = 2.5e-2
 
 
 @pytest.fixture(scope="module")

@@ -318,10 +318,18 @@ def test_a_toy_mixer_with_state_of_its_own(tmp_path):
             return [StateRequest((self.hidden,), torch.float32)]
 
         def forward(self, x, ctx, views, owns_cache):
-            state = views[0]                                  # [slots, hidden]
+            state = views[0]                                  # [slots + 1, hidden]; the last row is the padding slot's
             projected = x.float() @ self.weight.float().T
-            out = torch.empty_like(projected)
             plan = ctx.plan
+            if plan.is_decode:
+                # One token per sequence, row b for sequence b: from the device tables alone, so
+                # that a captured step can replay it. Padding sequences of such a step carry the
+                # padding slot: their (meaningless) state lands in the last row.
+                slot = ctx.tables.seq_slot.long()
+                current = self.decay * state[slot] + projected
+                state.index_copy_(0, slot, current)
+                return current.to(x.dtype)
+            out = torch.empty_like(projected)
             for b in range(plan.n_seqs):
                 slot, row0, count = int(plan.seq_slot[b]), int(plan.seq_row0[b]), int(plan.seq_len[b])
                 current = state[slot].clone()
@@ -380,4 +388,37 @@ def test_a_toy_mixer_with_state_of_its_own(tmp_path):
     slot = engine.acquire()                                              # a used slot: its state starts from zero
     got = engine.step(StepBatch([slot], [requests[2]], [list(range(64))])).cpu().numpy()
     assert np.abs(got - expected[2]).max() <= 5e-5 * max(1.0, np.abs(expected[2]).max())
+    engine.release(slot)
+    engine.cache.check()
+
+    # The same mixer inside the replayed decode graph, with a padding row: a bystander holds slot 0
+    # and keeps its state there while three other sequences decode in a captured step of four
+    # rows. The fourth row is padding; it carries the cache's padding slot, not slot 0, so the
+    # bystander's state is what its own tokens made it.
+    from kidi_b200.engine.decode_graph import DecodeSession
+    from kidi_b200.sampling.sampler import Sampler
+    taken = [engine.acquire(), engine.acquire()]
+    bystander = 0                                   # the slot a padding sequence must never stand for
+    assert bystander in taken
+    engine.release(taken[1 - taken.index(bystander)])
+    engine.step(StepBatch([bystander], [requests[2][:30]], [[]]))
+    others = [generator.integers(0, 256, size=n).tolist() for n in (12, 20, 33)]
+    wanted = [plain_toy_forward(config, tensors, tokens) for tokens in others]
+    slots = [engine.acquire() for _ in others]
+    heads = [len(tokens) - 6 for tokens in others]
+    engine.step(StepBatch(slots, [tokens[:head] for tokens, head in zip(others, heads)], [[], [], []]))
+    session = DecodeSession(engine, 4, Sampler(0), longest=64)
+    session.load(slots, [tokens[head] for tokens, head in zip(others, heads)], [0.0] * 3, [0, 1, 2], [1] * 3)
+    for step in range(6):
+        session.step([tokens[head + step] for tokens, head in zip(others, heads)])
+        logits = session.logits[:3].cpu().numpy()
+        for b in range(3):
+            reference = wanted[b][heads[b] + step]
+            assert np.abs(logits[b] - reference).max() <= 5e-5 * max(1.0, np.abs(reference).max()), (b, step)
+    after = engine.step(StepBatch([bystander], [requests[2][30:]], [list(range(34))])).cpu().numpy()
+    assert np.abs(after - expected[2][30:]).max() <= 5e-5 * max(1.0, np.abs(expected[2]).max()), \
+        "a padding row of the captured step changed the state of a sequence outside it"
+    assert engine.cache.padding_slot == engine.cache.n_slots
+    for held in [bystander, *slots]:
+        engine.release(held)
     engine.cache.check()

@@ -57,8 +57,8 @@ def test_a_random_configuration(tmp_path, record_property, seed):
     sizes = {key: config[key] for key in ("hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
                                           "intermediate_size", "vocab_size", "layer_types")}
     # Three times the largest differences measured over these twelve configurations on a B200
-    # (recorded by every run: `record_property`).
-    for dtype, tolerance in (("float32", 1e-5), ("bfloat16", 2.5e-2)):
+    # (1.9e-6 and 7.0e-3; every run records its own: `record_property`).
+    for dtype, tolerance in (("float32", 6e-6), ("bfloat16", 2.1e-2)):
         what = f"{sizes}, window {config.get('sliding_window')}, {dtype}"
         engine = Engine.load(folder, dtype=dtype, max_tokens=4096)
         whole = rh.run_whole(engine, requests)

@@ -34,9 +34,11 @@ def make_case(rows, heads, kv_heads, head_dim, lengths, seed):
     width = (heads + 2 * kv_heads) * head_dim
     qkv = torch.randn(rows, width, generator=generator).to(torch.bfloat16).to(DEVICE)
 
-    def arguments(out, splits, workspace):
+    def arguments(out, splits, workspace, whole_pages=False):
+        """`whole_pages`: the cache is told to be contiguous (cache_rows), so that the kernel takes
+        its pages by TMA tensor copies instead of row by row."""
         count = rows * heads * splits
-        return FastAttentionArgs(
+        block = FastAttentionArgs(
             qkv.data_ptr(), qkv.stride(0), 0, 0, qkv.stride(0), view.keys.data_ptr(), view.values.data_ptr(),
             cache_geometry(view, kv_heads, head_dim), out.data_ptr(), out.stride(0),
             tables["row_seq"].data_ptr(), tables["row_pos"].data_ptr(), tables["seq_slot"].data_ptr(),
@@ -44,6 +46,9 @@ def make_case(rows, heads, kv_heads, head_dim, lengths, seed):
             rows, rows, heads, kv_heads, 0, 1.0 / math.sqrt(head_dim),
             workspace.data_ptr() if workspace is not None else 0,
             workspace.data_ptr() + count * head_dim * 4 if workspace is not None else 0, splits, 0)
+        if whole_pages:
+            block.cache_rows = view.keys.numel() // head_dim
+        return block
 
     return arguments, (cache, tables, qkv)
 
@@ -61,17 +66,19 @@ def test_static_workspace_matches_the_allocating_entry_point():
 
     cases = [dict(rows=6, heads=16, kv_heads=4, lengths=[1000, 64, 65, 333, 1, 700], splits=7, seed=1),
              dict(rows=3, heads=8, kv_heads=8, lengths=[129, 900, 400], splits=3, seed=2)]
-    for case in cases:
+    # Each case twice: pages copied row by row, then whole pages by TMA (both forms of the kernel
+    # merge their splits through the fixed workspace).
+    for case, whole_pages in [(case, form) for case in cases for form in (False, True)]:
         rows, heads, splits = case["rows"], case["heads"], case["splits"]
         arguments, keep = make_case(rows, heads, case["kv_heads"], head_dim, case["lengths"], case["seed"])
         need = lib.kidi_attention_decode_static_need(rows, heads, splits)
         assert need == rows * heads * splits * (head_dim + 2)
         expected = torch.zeros(rows, heads * head_dim, dtype=torch.bfloat16, device=DEVICE)
         workspace = torch.empty(need, dtype=torch.float32, device=DEVICE)
-        block = arguments(expected, splits, workspace)
+        block = arguments(expected, splits, workspace, whole_pages)
         assert lib.kidi_attention_decode(ctypes.byref(block), stream) == 0
         found = torch.zeros_like(expected)
-        block = arguments(found, splits, None)                     # no workspace from the caller
+        block = arguments(found, splits, None, whole_pages)        # no workspace from the caller
         assert lib.kidi_attention_decode_static(ctypes.byref(block), stream) == 0
         torch.cuda.synchronize()
         assert torch.isfinite(found.float()).all()
@@ -85,3 +92,8 @@ def test_static_workspace_matches_the_allocating_entry_point():
     block = arguments(out, 1, None)
     block.rows, block.splits = 60000, 64                           # 60000 * 8 * 64 * 130 floats: far too many
     assert lib.kidi_attention_decode_static(ctypes.byref(block), stream) == -3
+    # Sizes whose product would not fit 64 bits are refused before it is formed.
+    assert lib.kidi_attention_decode_static_need(2**31 - 1, 2**31 - 1, 2**31 - 1) == -1
+    block.rows, block.heads, block.splits = 2**31 - 1, 2**31 - 1, 2**31 - 1
+    assert lib.kidi_attention_decode_static(ctypes.byref(block), stream) == -3
+    torch.cuda.synchronize()
