@@ -337,7 +337,10 @@ class AttentionLauncher:
     def run(self, ctx, qkv, out, **arguments) -> None:
         run(ctx, qkv, out, scale=self.scale, window=self.window, **self.geometry, **arguments)
 
-    def launch_signature(self, rows: int, longest: int, device: torch.device) -> tuple:
-        """What a captured decode step freezes of this launcher's choices."""
+    def launch_signature(self, dtype: torch.dtype, rows: int, longest: int, device: torch.device) -> tuple:
+        """What a captured decode step freezes of this launcher's choices: the form of the
+        tensor-core decode kernel (the general kernel, which the 32-bit engine runs, has none)."""
         geometry = self.geometry
+        if not fast_fits(dtype, geometry["heads"], geometry["kv_heads"], geometry["head_dim"], True):
+            return ()
         return decode_form(rows, geometry["kv_heads"], geometry["head_dim"], longest, self.window, device)

@@ -96,7 +96,7 @@ class Attention(Part):
     def launch_signature(self, rows: int, longest: int) -> tuple:
         """The choices a captured decode step of `rows` sequences of at most `longest` tokens
         freezes for this part (the form of its decode kernel)."""
-        return self.launcher.launch_signature(rows, longest, self.env.device)
+        return self.launcher.launch_signature(self.env.dtype, rows, longest, self.env.device)
 
     def forward(self, x: torch.Tensor, ctx, views, owns_cache: bool) -> torch.Tensor:
         view = views[0]

@@ -78,6 +78,29 @@ def test_greedy_generation_in_bfloat16(model_folders, name):
     assert close_calls <= len(prompts) * 12 // 4, "too many tokens are decided within the rounding error to test much"
 
 
+def test_a_longer_call_gets_a_capture_of_its_own(model_folders):
+    """The captured decode step freezes how attention splits a sequence's keys, chosen from the
+    longest sequence the call may come to hold. A second call with much longer sequences must
+    not replay the first call's graph: it captures one fitted to its own length, and both give
+    the plain model's tokens."""
+    config, tensors = plain_model.read_model_folder(model_folders["tiny_e"])
+    generator = np.random.default_rng(8)
+    engine = load(model_folders["tiny_e"], "float32", max_tokens=2048)
+    bf16 = load(model_folders["tiny_e"], "bfloat16", max_tokens=2048)
+    short = [generator.integers(0, config["vocab_size"], size=n).tolist() for n in (5, 9)]
+    long = [generator.integers(0, config["vocab_size"], size=n).tolist() for n in (300, 340)]
+    for prompts in (short, long, short):
+        found = engine.generate(prompts, max_new_tokens=6, ignore_eos=True)
+        assert found == [plain_model.generate(config, tensors, prompt, 6) for prompt in prompts]
+        assert bf16.generate(prompts, max_new_tokens=6, ignore_eos=True) == \
+            bf16.generate(prompts, max_new_tokens=6, ignore_eos=True, use_graph=False)
+    sessions = next(iter(bf16._backends.values()))._sessions
+    signatures = [key[1] for key in sessions]
+    assert len(sessions) == 2 and signatures[0] != signatures[1], "the longer call replayed the shorter call's capture"
+    assert all(key[0] == 2 for key in sessions)                    # one batch bucket, two launch signatures
+    assert len(next(iter(engine._backends.values()))._sessions) == 1   # the 32-bit kernels choose nothing by length
+
+
 def test_stop_tokens_end_a_sequence_early(model_folders):
     """A stop token chosen from what the model really generates: the sequence ends there,
     the token is not returned, and the others go on."""

@@ -233,6 +233,63 @@ def test_the_bfloat16_comparison_notices_swapped_pages(model_folders, references
             f"{name}: swapped cache pages of {request} stay within the bfloat16 tolerance"
 
 
+@pytest.mark.parametrize("name", list(ALL))
+def test_the_bfloat16_engine_against_the_32_bit_engine(model_folders, references, name):
+    """The same cuts in both engines, compared with each other at the bfloat16 bound: the 32-bit
+    engine shares its tables, cache and step function with the bfloat16 one and none of its
+    product or attention kernels."""
+    requests, _ = references[name]
+    wide = make_engine(model_folders[name], "float32")
+    narrow = make_engine(model_folders[name], "bfloat16")
+    bound = tolerance("bfloat16", name)
+    for what, run in (("whole", rh.run_whole), ("last 32 one by one", lambda e, r: rh.run_tail_decoded(e, r, 32)),
+                      ("batches of 3", lambda e, r: rh.run_batches(e, r, batch_size=3, prompt_fraction=0.4)),
+                      ("chunks of 100", lambda e, r: rh.run_chunked(e, r, chunk=100))):
+        rh.assert_matches(run(narrow, requests), run(wide, requests), bound, f"{name} bfloat16 against 32-bit, {what}")
+
+
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_e"])
+def test_folders_stored_in_32_bit_and_in_shards(model_folders, references, tmp_path, name):
+    """The same weights stored as float32 (what the file holds is the bfloat16 values, widened),
+    and spread over three shards behind model.safetensors.index.json: every engine reads them to
+    the same logits. A bfloat16 engine keeps 32-bit matrices 32-bit and says so; asked to, it
+    rounds them and then computes what it computes from the bfloat16 folder, bit for bit."""
+    import shutil
+    from kidi_b200 import Engine
+    from kidi_b200.weights.safetensors_io import SafetensorsFile, write_safetensors
+    requests, expected = references[name]
+    requests = dict(list(requests.items())[:4])
+    expected = {request: expected[request] for request in requests}
+    source = SafetensorsFile(os.path.join(model_folders[name], "model.safetensors"))
+    tensors = {tensor: source.tensor(tensor).clone() for tensor in source.names()}
+    source.close()
+    wide_folder, sharded_folder = tmp_path / "wide", tmp_path / "sharded"
+    for folder in (wide_folder, sharded_folder):
+        folder.mkdir()
+        shutil.copy(os.path.join(model_folders[name], "config.json"), folder / "config.json")
+    write_safetensors(str(wide_folder / "model.safetensors"), {n: t.float() for n, t in tensors.items()})
+    names = sorted(tensors)
+    weight_map = {}
+    for index in range(3):
+        file = f"model-{index + 1:05d}-of-00003.safetensors"
+        members = names[index::3]
+        write_safetensors(str(sharded_folder / file), {n: tensors[n] for n in members})
+        weight_map.update({n: file for n in members})
+    (sharded_folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+
+    reference = rh.run_whole(make_engine(model_folders[name], "bfloat16"), requests)
+    sharded = Engine.load(str(sharded_folder), dtype="bfloat16", max_tokens=2048)
+    assert all(np.array_equal(found, reference[request]) for request, found in rh.run_whole(sharded, requests).items())
+    wide32 = Engine.load(str(wide_folder), dtype="float32", max_tokens=2048)
+    rh.assert_matches(rh.run_tail_decoded(wide32, requests, 32), expected, FP32_TOLERANCE, "float32 folder, 32-bit engine")
+    with pytest.warns(UserWarning, match="32-bit kernel"):
+        kept = Engine.load(str(wide_folder), dtype="bfloat16", max_tokens=2048)
+    rh.assert_matches(rh.run_batches(kept, requests, batch_size=3), expected, tolerance("bfloat16", name, rms=False),
+                      "float32 folder, bfloat16 engine with 32-bit weights")
+    cast = Engine.load(str(wide_folder), dtype="bfloat16", max_tokens=2048, cast_weights=True)
+    assert all(np.array_equal(found, reference[request]) for request, found in rh.run_whole(cast, requests).items())
+
+
 def test_padding_changes_nothing(model_folders):
     """A request's logits are the same alone and beside a much longer neighbour."""
     name = "tiny_a"
