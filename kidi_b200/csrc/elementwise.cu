@@ -290,3 +290,31 @@ KIDI_API int kidi_add_bias(void* y, int dtype, const float* bias, int rows, int 
         return kidi_launch(add_bias_kernel<bf16>, blocks, threads, 0, stream, (bf16*)y, bias, total, features, ldy);
     return KIDI_REFUSED_DTYPE;
 }
+
+// out[r, :] = values[r, :] * 1 / sqrt(sum(parts[r, :count]) / width + eps): rows that a product stored
+// without their norm's factor (gemm_skinny.cu, "into the residual"), for a consumer that wants plain rows.
+// The parts are added in the order the weight-streaming product adds them (a warp: lane l takes parts
+// l, l + 32, ..., then the fixed tree), so both consumers see the same factor.
+__global__ void __launch_bounds__(256)
+apply_row_factors_kernel(const bf16* __restrict__ values, long long ld, const float* __restrict__ parts, int count,
+                         int stride, int width, float eps, bf16* __restrict__ out, int hidden) {
+    __shared__ float factor;
+    const int r = blockIdx.x;
+    if (threadIdx.x < 32) {
+        float square = 0.f;
+        for (int b = threadIdx.x; b < count; b += 32) square += parts[(long long)r * stride + b];   // ascending, as there
+        square = warp_sum(square);
+        if (threadIdx.x == 0) factor = 1.0f / sqrtf(square / (float)width + eps);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < hidden; c += 256)
+        out[(long long)r * hidden + c] = from_float<bf16>(to_float(values[r * ld + c]) * factor);
+}
+
+KIDI_API int kidi_apply_row_factors(const void* values, long long ld, const float* parts, int count, int stride,
+                                    int width, float eps, void* out, int rows, int hidden, cudaStream_t stream) {
+    if (rows <= 0 || hidden <= 0) return 0;
+    if (count < 1 || stride < count || width < 1) return KIDI_REFUSED_SIZE;
+    return kidi_launch(apply_row_factors_kernel, rows, 256, 0, stream, (const bf16*)values, ld, parts, count, stride,
+                       width, eps, (bf16*)out, hidden);
+}

@@ -110,7 +110,13 @@ class CausalLM:
         for position in self.env.positions.values():
             position.on_embeddings(stream, ctx)
         for index, entry in enumerate(self.schedule):
-            self.layers[entry.layer].forward(stream, ctx, ctx.cache.views(index), entry.cache_from is None)
+            layer = self.layers[entry.layer]
+            options = {}
+            if getattr(layer, "supports_next_norm", False) and index + 1 < len(self.schedule):
+                # The norm that reads the stream next: the layer's last product may prepare its rows.
+                following = self.layers[self.schedule[index + 1].layer]
+                options["next_norm"] = following.first_norm() if hasattr(following, "first_norm") else None
+            layer.forward(stream, ctx, ctx.cache.views(index), entry.cache_from is None, **options)
         if ctx.plan.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.env.device)
         normed = self.final_norm.forward(stream, rows=ctx.tables.want_rows)

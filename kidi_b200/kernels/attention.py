@@ -142,7 +142,8 @@ def fast_fits(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, deco
 
 
 def sm_count(device: torch.device) -> int:
-    index = device.index if device.index is not None else torch.cuda.current_device()
+    index = device.index if device.index is not None else \
+        (torch.cuda.current_device() if torch.cuda.is_available() else 0)
     if index not in _sm_count:
         _sm_count[index] = torch.cuda.get_device_properties(index).multi_processor_count
     return _sm_count[index]

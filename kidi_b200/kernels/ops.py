@@ -102,6 +102,8 @@ def core():
         lib.kidi_gemm_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                        c_longlong, c_longlong, c_longlong, c_void_p, c_void_p]
         lib.kidi_add_bias.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p]
+        lib.kidi_apply_row_factors.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
+                                               c_int, c_int, c_void_p]
         lib.kidi_rope_store.argtypes = [c_void_p, c_int, c_int, c_void_p]
         lib.kidi_attention_generic.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_argmax.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
@@ -112,7 +114,7 @@ def core():
         lib.kidi_advance_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_void_p]
         for name in ("kidi_embedding", "kidi_add_rmsnorm", "kidi_silu_gate", "kidi_gemm_simt", "kidi_add_bias",
-                     "kidi_rope_store",
+                     "kidi_apply_row_factors", "kidi_rope_store",
                      "kidi_attention_generic", "kidi_argmax", "kidi_sample", "kidi_advance_decode"):
             getattr(lib, name).restype = c_int
         _core = lib
@@ -222,6 +224,21 @@ def add_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
     _check(core().kidi_add_bias(_ptr(y), dtype_code(y.dtype), _ptr(bias), y.shape[0], y.shape[1], y.stride(0),
                                 _stream()), "add_bias")
     return y
+
+
+def apply_row_factors(values: torch.Tensor, parts: torch.Tensor, width: int, eps: float) -> torch.Tensor:
+    """values[r, :] / sqrt(sum(parts[r, :]) / width + eps) as a new bfloat16 matrix: rows that were stored
+    without their norm's factor, made plain."""
+    _need_cuda(values, parts)
+    if values.dtype != torch.bfloat16 or values.dim() != 2 or values.stride(1) != 1:
+        raise invalid_argument("apply_row_factors takes a bfloat16 matrix with contiguous rows")
+    if parts.dtype != torch.float32 or parts.dim() != 2 or parts.shape[0] != values.shape[0] or parts.stride(1) != 1:
+        raise invalid_argument("apply_row_factors takes float32 parts, one row of them per row of values")
+    out = torch.empty(values.shape, dtype=torch.bfloat16, device=values.device)
+    _check(core().kidi_apply_row_factors(_ptr(values), values.stride(0), _ptr(parts), parts.shape[1], parts.stride(0),
+                                         int(width), float(eps), _ptr(out), values.shape[0], values.shape[1],
+                                         _stream()), "apply_row_factors")
+    return out
 
 
 def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,

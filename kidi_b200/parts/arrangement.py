@@ -6,14 +6,44 @@ Each sum is handed to the stream as a pending delta and formed by the next norm,
 32-bit.
 
 Interface of an arrangement: `__init__(spec, env, parts)` with the layer's parts by
-role name, `children()`, and `forward(stream, ctx, views, owns_cache)`.
+role name, `children()`, and `forward(stream, ctx, views, owns_cache)`. Optionally
+`first_norm()` (the norm it applies to the stream first) and, with the class attribute
+`supports_next_norm`, `forward(..., next_norm=...)`: the norm that reads the stream after
+this layer, so that the layer's last product can prepare the rows for it.
+
+Norms between two products need no launch of their own when both products run on the
+weight-streaming kernel (`ResidualSink`, `RowScaled` in parts/base.py): the product before
+the norm adds its result to the stream and prepares the rows, the product after applies
+each row's factor. The arrangement only makes the offers; parts that do not know them
+get and return plain matrices.
 """
 from __future__ import annotations
 
 from typing import Dict
 
-from .base import Part, ResidualStream
+from .base import Part, ResidualSink, ResidualStream, plain_rows
 from .registry import register_part
+
+
+import os
+
+# Which norms are folded into the products around them: "all", "post" (the norm after the mixer only),
+# "none".
+FOLD_NORMS = os.environ.get("KIDI_B200_FOLD_NORMS", "all")
+
+
+def normed_for(norm: Part, stream: ResidualStream, consumer: Part):
+    """The stream's rows normalised by `norm`, as a `RowScaled` where `consumer` takes one."""
+    if getattr(consumer, "accepts_row_scaled", False) and hasattr(norm, "prepared_weight"):
+        return norm.forward(stream, scaled=True)
+    return plain_rows(norm.forward(stream))
+
+
+def sink_for(part: Part, stream: ResidualStream, norm):
+    """The offer to `part` to add its result to the stream itself, for `norm` to find prepared."""
+    if norm is not None and FOLD_NORMS != "none" and getattr(part, "takes_sink", False) and hasattr(norm, "prepared_weight"):
+        return {"sink": ResidualSink(stream, norm)}
+    return {}
 
 
 @register_part("arrangement", "pre_norm")
@@ -33,6 +63,13 @@ class PreNormBlock(Part):
     def cache_requests(self) -> list:
         return self.mixer.cache_requests()
 
-    def forward(self, stream: ResidualStream, ctx, views, owns_cache: bool) -> None:
-        stream.add(self.mixer.forward(self.input_norm.forward(stream), ctx, views, owns_cache))
-        stream.add(self.feed_forward.forward(self.post_norm.forward(stream), ctx))
+    supports_next_norm = True
+
+    def first_norm(self) -> Part:
+        return self.input_norm
+
+    def forward(self, stream: ResidualStream, ctx, views, owns_cache: bool, next_norm=None) -> None:
+        stream.add(self.mixer.forward(normed_for(self.input_norm, stream, self.mixer), ctx, views, owns_cache,
+                                      **sink_for(self.mixer, stream, self.post_norm)))
+        stream.add(self.feed_forward.forward(normed_for(self.post_norm, stream, self.feed_forward), ctx,
+                                             **sink_for(self.feed_forward, stream, next_norm if FOLD_NORMS == "all" else None)))

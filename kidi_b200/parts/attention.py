@@ -33,6 +33,9 @@ from .spec import ParamSpec
 
 @register_part("mixer", "attention")
 class Attention(Part):
+    accepts_row_scaled = True     # x may lack its norm's factor: the q/k/v product applies it
+    takes_sink = True             # the output product may add its result to the residual stream itself
+
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.hidden = int(spec.param("hidden_size"))
@@ -98,7 +101,7 @@ class Attention(Part):
         freezes for this part (the form of its decode kernel)."""
         return self.launcher.launch_signature(self.env.dtype, rows, longest, self.env.device)
 
-    def forward(self, x: torch.Tensor, ctx, views, owns_cache: bool) -> torch.Tensor:
+    def forward(self, x, ctx, views, owns_cache: bool, sink=None) -> Optional[torch.Tensor]:
         view = views[0]
         plan = ctx.plan
         qkv = self.qkv.forward(x)
@@ -128,4 +131,4 @@ class Attention(Part):
         if owns_cache and not store_first:
             ops.rope_store(qkv, q_norm=None, k_norm=None, eps=self.eps, tables=ctx.tables, kv_view=view, store=True,
                            transform=False, cos=None, sin=None, rotary_dim=0, **common)
-        return self.out.forward(attended)
+        return self.out.forward(attended, sink=sink)

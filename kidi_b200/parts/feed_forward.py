@@ -15,7 +15,7 @@ import torch
 
 from ..errors import unsupported
 from ..kernels import ops
-from .base import Part
+from .base import Part, RowScaled
 from .linear import Linear
 from .registry import register_part
 from .spec import ParamSpec
@@ -23,6 +23,9 @@ from .spec import ParamSpec
 
 @register_part("feed_forward", "gated_mlp")
 class GatedFeedForward(Part):
+    accepts_row_scaled = True     # x may lack its norm's factor: the gate/up product applies it
+    takes_sink = True             # the down product may add its result to the residual stream itself
+
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.hidden = int(spec.param("hidden_size"))
@@ -45,12 +48,18 @@ class GatedFeedForward(Part):
         self.gate_up = Linear(tensors["gate_up_proj.weight"])
         self.down = Linear(tensors["down_proj.weight"])
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    def forward(self, x, ctx, sink=None) -> Optional[torch.Tensor]:
         from ..kernels import skinny, tcgen05
-        if skinny.fits(x, self.gate_up.weight):
-            gated = skinny.gemm_silu_gate(x, self.gate_up.weight)
+        factors = None
+        if isinstance(x, RowScaled):
+            if skinny.supports(x.values, self.gate_up.weight) and x.values.shape[0] <= skinny.MAX_ROWS:
+                x, factors = x.values, x.factors
+            else:
+                x = x.plain()
+        if factors is not None or skinny.fits(x, self.gate_up.weight):
+            gated = skinny.gemm_silu_gate(x, self.gate_up.weight, factors=factors)
         elif tcgen05.MIN_GATED_ROWS <= x.shape[0] <= tcgen05.MAX_GATED_ROWS and tcgen05.fits(x, self.gate_up.weight):
             gated = tcgen05.gemm_silu_gate(x, self.gate_up.weight)
         else:
             gated = ops.silu_gate(self.gate_up.forward(x))
-        return self.down.forward(gated)
+        return self.down.forward(gated, sink=sink)

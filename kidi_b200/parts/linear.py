@@ -26,6 +26,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
+from .base import RowScaled
 
 
 class Linear:
@@ -38,13 +39,35 @@ class Linear:
             raise ValueError("a linear bias has one element per output feature")
         self.bias = bias.float().contiguous() if bias is not None else None
 
-    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        out_dtype = out_dtype or x.dtype
+    def forward(self, x, out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
+                sink=None) -> Optional[torch.Tensor]:
+        """`x`: a matrix or a `RowScaled` (rows that lack their norm's factor: the weight-streaming
+        kernel applies it to its result, any other kernel gets plain rows). `sink`: a
+        `ResidualSink`; if the weight-streaming kernel runs and the sink's norm takes prepared
+        rows, the result goes into the residual stream and None is returned."""
+        from ..kernels import skinny
         weight, bias = self.weight, self.bias
+        factors = None
+        if isinstance(x, RowScaled):
+            if skinny.supports(x.values, weight) and x.values.shape[0] <= skinny.MAX_ROWS:
+                x, factors = x.values, x.factors
+            else:
+                x = x.plain()
+        out_dtype = out_dtype or x.dtype
+        if sink is not None and out is None and out_dtype == x.dtype and skinny.supports(x, weight) \
+                and x.shape[0] <= skinny.MAX_ROWS:
+            norm_weight = sink.norm.prepared_weight() if hasattr(sink.norm, "prepared_weight") else None
+            stream = sink.stream
+            if norm_weight is not None and stream.pending is None and stream.hidden.shape == (x.shape[0], weight.shape[0]):
+                values, parts = skinny.gemm_into_residual(x, weight, stream.hidden, norm_weight, bias=bias,
+                                                          factors=factors)
+                stream.prepared = (sink.norm, values, parts)
+                return None
+        if factors is not None:
+            return skinny.gemm(x, weight, out_dtype, out=out, bias=bias, factors=factors)
         if x.dtype == torch.float32 or weight.dtype == torch.float32:
             return ops.gemm_simt(x, weight, out_dtype, out=out, bias=bias)
-        from ..kernels import skinny, tcgen05
+        from ..kernels import tcgen05
         if skinny.fits(x, weight):
             return skinny.gemm(x, weight, out_dtype, out=out, bias=bias)
         if weight.shape[0] >= tcgen05.MIN_FEATURES and tcgen05.fits(x, weight):

@@ -149,6 +149,52 @@ def test_gemm_tcgen05_silu_gate(rows, splits):
     assert tcgen05.error_code(torch.device(DEVICE)) == 0
 
 
+@pytest.mark.parametrize("rows", [1, 5, 8])
+@pytest.mark.parametrize("shape", [(389, 96, 200), (4096, 1024, 520), (48, 4104, 64)])
+@pytest.mark.parametrize("norm_dtype", [torch.bfloat16, torch.float32])
+def test_the_norm_between_two_products_without_a_kernel_of_its_own(rows, shape, norm_dtype):
+    """The product before an RMSNorm adds its result to the residual stream and leaves the rows
+    times the norm's weight and the parts of their sums of squares; the product after applies
+    each row's factor (plain and with the SiLU gate); `apply_row_factors` makes plain rows.
+    Against the plain residual sum, norm and products in 64-bit."""
+    from kidi_b200.kernels import ops, skinny
+    N, K, N2 = shape
+    eps = 1e-5
+    generator = torch.Generator().manual_seed(rows * 7 + N)
+    x = torch.randn(rows, K, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=generator) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=generator)
+    residual = torch.randn(rows, N, generator=generator) * 2
+    norm_weight = (1 + 0.1 * torch.randn(N, generator=generator)).to(norm_dtype)
+    w2 = (torch.randn(2 * N2, N, generator=generator) / math.sqrt(N)).to(torch.bfloat16)
+    summed = residual.double() + x.double() @ w.double().T + bias.double()
+    normed = plain_model.rms_norm(summed, norm_weight.double(), eps)
+
+    device_residual = residual.to(DEVICE)
+    values, parts = skinny.gemm_into_residual(x.to(DEVICE), w.to(DEVICE), device_residual, norm_weight.to(DEVICE),
+                                              bias=bias.to(DEVICE))
+    assert values.shape == (rows, N) and parts.shape == (rows, -(-N // 16))
+    close(device_residual, summed, 2e-5, "the residual stream after the product")
+    close(parts.double().sum(dim=1), (summed * summed).sum(dim=1), 1e-5, "sums of squares")
+    close(values, summed * norm_weight.double(), 5e-3, "rows times the norm's weight")
+    close(ops.apply_row_factors(values, parts, N, eps), normed, 8e-3, "plain rows")
+    factors = (parts, N, eps)
+    if N % 8 == 0:
+        expected = normed @ w2.double().T
+        close(skinny.gemm(values, w2.to(DEVICE), torch.bfloat16, factors=factors), expected, 1e-2, "product with row factors")
+        gate, up = expected[:, :N2], expected[:, N2:]
+        close(skinny.gemm_silu_gate(values, w2.to(DEVICE), factors=factors), gate / (1 + torch.exp(-gate)) * up, 1e-2,
+              "gated product with row factors")
+        # A second product into the residual, fed with rows that lack their factor (as a layer's last
+        # product is when it follows a prepared norm).
+        back = (torch.randn(N, N, generator=generator) / math.sqrt(N)).to(torch.bfloat16)
+        again_values, again_parts = skinny.gemm_into_residual(values, back.to(DEVICE), device_residual,
+                                                              norm_weight.to(DEVICE), factors=factors)
+        twice = summed + normed @ back.double().T
+        close(device_residual, twice, 8e-3, "a product with row factors into the residual")
+        close(again_parts.double().sum(dim=1), (twice * twice).sum(dim=1), 2e-2, "its sums of squares")
+
+
 @pytest.mark.parametrize("rows,shape", [(1, (389, 96)), (8, (4096, 1024)), (13, (130, 200)), (300, (389, 96))])
 def test_products_with_a_bias(rows, shape):
     """y = x W^T + b in every product kernel (the bias in 32-bit, added in the epilogue) and

@@ -63,7 +63,10 @@ def test_which_product_a_shape_goes_to():
         return (torch.empty(rows, width, dtype=torch.bfloat16, device="meta"),
                 torch.empty(features, width, dtype=torch.bfloat16, device="meta"))
     assert skinny.fits(*operands(8, 4096)) and skinny.fits(*operands(1, 24576))
-    assert not skinny.fits(*operands(8, 6144))                    # between one and 3.5 waves of blocks: the library
+    assert skinny.fits(*operands(8, 6144))
+    assert skinny._row_tiles(6144, 8, DEVICE) == 4                # 1.3 rounds of heavy blocks on 148 SMs: light blocks
+    assert skinny._row_tiles(4096, 8, DEVICE) == 1 and skinny._row_tiles(24576, 8, DEVICE) == 1
+    assert skinny._row_tiles(6144, 9, DEVICE) == 1
     assert not skinny.fits(*operands(9, 4096))
     assert not skinny.fits(*operands(8, 4096, width=4100))        # rows that 16-byte vectors cannot read
     assert tcgen05.fits(*operands(16, 24576)) and not tcgen05.fits(*operands(17, 24576))
