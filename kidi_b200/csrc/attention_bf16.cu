@@ -50,11 +50,11 @@ constexpr size_t DECODE_SHARED = DECODE_TILES > DECODE_MERGE ? DECODE_TILES : DE
 // behind its tiles what the other blocks of a cluster send it: [splits][share] partial
 // values and [8 splits][8 heads] maxima and denominators. Three blocks of head width 128
 // fit an SM.
-constexpr int NARROW_RECV_OUT_FLOATS = 8 * D + 8;
+constexpr int NARROW_RECV_OUT_FLOATS = 8 * D + 8 * 4;    // [splits][share], share rounded up to four
 constexpr int NARROW_RECV_FLOATS = NARROW_RECV_OUT_FLOATS + 8 * 8 * 2;
 constexpr size_t NARROW_TILES = (size_t)(8 + 4 * TILE) * PITCH * sizeof(bf16);
 constexpr size_t NARROW_MERGE =
-    (size_t)8 * PITCH * sizeof(bf16) + (size_t)(4 * 8 * D + 4 * 8 * 2 + 2 * 8 * 32 + 8) * sizeof(float);
+    (size_t)8 * PITCH * sizeof(bf16) + (size_t)(4 * 8 * (D + 4) + 4 * 8 * 2 + 2 * 8 * 32 + 8) * sizeof(float);
 constexpr size_t NARROW_TILE_BYTES = ((NARROW_TILES > NARROW_MERGE ? NARROW_TILES : NARROW_MERGE) + 15) / 16 * 16;
 constexpr size_t NARROW_SHARED = NARROW_TILE_BYTES + NARROW_RECV_FLOATS * sizeof(float);
 // The swizzled form: four unpadded tiles on a 1024-byte boundary, then the query rows (the
@@ -64,7 +64,7 @@ constexpr size_t SWIZZLED_SHARED = 1024 + SWIZZLED_TILE_BYTES + NARROW_RECV_FLOA
 // The ring form of it: three tiles.
 constexpr size_t RING_TILE_BYTES = ((size_t)(3 * TILE * D + 8 * PITCH) * sizeof(bf16) + 15) / 16 * 16;
 constexpr size_t RING_SHARED = 1024 + RING_TILE_BYTES + NARROW_RECV_FLOATS * sizeof(float);
-static_assert((size_t)(4 * 8 * D + 4 * 8 * 2 + 2 * 8 * 32 + 8) * sizeof(float) <= (size_t)3 * TILE * D * sizeof(bf16) || D % 64,
+static_assert((size_t)(4 * 8 * (D + 4) + 4 * 8 * 2 + 2 * 8 * 32 + 8) * sizeof(float) <= (size_t)3 * TILE * D * sizeof(bf16) || D % 64,
               "the warps' partial results fit the tiles");
 
 __device__ __forceinline__ unsigned smem_address(const void* pointer) {
@@ -614,7 +614,7 @@ __device__ __forceinline__ float head_square_sum(uint4 own) {
 // cache held before (zeros or an earlier sequence's finite values), and their weights
 // are exact zeros.
 template <bool CLUSTER, int FORM>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 4)     // four blocks an SM where shared memory allows (the ring form; narrow heads)
 attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                                Args a) {
     constexpr bool SWIZZLED = FORM != 0, RING = FORM == 2;
@@ -647,10 +647,14 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
 
+    // A step of one token per sequence has row b for sequence b: the position and the slot are asked
+    // for together with the row's sequence instead of after it (one trip instead of two).
+    const int guess = row < a.seqs ? row : 0;
+    const int position_ahead = a.row_pos[row], slot_ahead = a.seq_slot[guess];
     int tiles = 0, tile_first = 0, position = 0, low = 0, slot = 0;
     if (seq >= 0) {
-        position = a.row_pos[row];
-        slot = a.seq_slot[seq];
+        position = position_ahead;
+        slot = seq == guess ? slot_ahead : a.seq_slot[seq];
         low = a.window > 0 ? max(0, position - a.window + 1) : 0;
         const int tile_low = low / TILE, tile_high = position / TILE;
         const int all = tile_high - tile_low + 1;
@@ -659,7 +663,14 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
         tiles = max(0, min(per_split, tile_high + 1 - tile_first));
     }
     __shared__ unsigned long long tile_bar[3];
+    constexpr int PAGES_AHEAD = 16;                          // (four blocks of the ring form fill an SM to 200 bytes)
+    __shared__ int page_of[PAGES_AHEAD];                     // the pages of the block's first tiles
     if (tiles > 0) {
+        if (SWIZZLED && threadIdx.x < min(tiles, PAGES_AHEAD)) {   // all at once, not one look-up before each copy
+            int page_index = tile_first + threadIdx.x;
+            if (a.cache.ring_pages) page_index %= a.cache.ring_pages;
+            page_of[threadIdx.x] = a.cache.table[(long long)slot * a.cache.pages_per_seq + page_index];
+        }
         if (threadIdx.x == 0) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&tile_bar[0])));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_address(&tile_bar[1])));
@@ -675,12 +686,17 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
         auto rows_to_copy = [&](int tile) {
             return min(TILE, position - tile * TILE + 1) - (a.fuse != 0 && tile == new_tile ? 1 : 0);
         };
+        // The first row of the block's tile `index` in the cache seen as [rows, D] (pages of 64 rows).
+        auto page_row_of = [&](int index) -> int {
+            if (index < PAGES_AHEAD) return (page_of[index] * a.cache.kv_heads + kv_head) * TILE;
+            return (int)(cache_row_offset(a.cache, slot, (tile_first + index) * TILE, kv_head) / D);
+        };
         // The first two tiles are asked for before anything else: the kernel's time is the
         // time its keys and values take to arrive.
         auto issue = [&](int tile, int buffer) {
             if (SWIZZLED) {
                 if (threadIdx.x == 0) {         // one copy per 64 columns of the key page and of the value page
-                    const int page_row = (int)(cache_row_offset(a.cache, slot, tile * TILE, kv_head) / D);
+                    const int page_row = page_row_of(tile - tile_first);
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
                                      smem_address(&tile_bar[buffer])),
                                  "r"((unsigned)(2 * TILE * D * 2))
@@ -704,7 +720,7 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
         auto issue_load = [&](int load) {
             if (threadIdx.x == 0) {
                 const int buffer = load % 3;
-                const int page_row = (int)(cache_row_offset(a.cache, slot, (tile_first + (load >> 1)) * TILE, kv_head) / D);
+                const int page_row = page_row_of(load >> 1);
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
                                  smem_address(&tile_bar[buffer])),
                              "r"((unsigned)(TILE * D * 2))
@@ -895,9 +911,11 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
         denom[i] += __shfl_xor_sync(0xffffffffu, denom[i], 16);
     }
 
-    // Merge the four warps in warp order through shared memory (the tiles are free now).
-    float* merge_out = reinterpret_cast<float*>(k_tiles);                // [4][8][D]
-    float* merge_stat = merge_out + 4 * 8 * D;                           // [4][8][2]
+    // Merge the four warps in warp order through shared memory (the tiles are free now). Rows of
+    // the partial results are padded by four floats: the 32 lanes of a store hit 32 banks.
+    constexpr int MP = D + 4;
+    float* merge_out = reinterpret_cast<float*>(k_tiles);                // [4][8][MP]
+    float* merge_stat = merge_out + 4 * 8 * MP;                          // [4][8][2]
     // What the other blocks of a cluster send (never used for anything else: a block that is
     // ahead may send while this one still works on its tiles).
     float* recv_out = reinterpret_cast<float*>(raw + (RING ? RING_TILE_BYTES : SWIZZLED ? SWIZZLED_TILE_BYTES : NARROW_TILE_BYTES));   // [splits][share]
@@ -905,68 +923,85 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
     cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
     __syncthreads();
 #pragma unroll
-    for (int n = 0; n < D / 16; ++n) {
-        merge_out[(warp * 8 + 2 * t) * D + n * 16 + g] = o[n][0];
-        merge_out[(warp * 8 + 2 * t + 1) * D + n * 16 + g] = o[n][1];
-        merge_out[(warp * 8 + 2 * t) * D + n * 16 + g + 8] = o[n][2];
-        merge_out[(warp * 8 + 2 * t + 1) * D + n * 16 + g + 8] = o[n][3];
-    }
-    if (g == 0) {
+    for (int i = 0; i < 2; ++i) {                                        // heads 2t and 2t + 1 of this lane
+        const int head = 2 * t + i;
+        if (head < group) {
+            float* mine = merge_out + (warp * 8 + head) * MP;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            merge_stat[(warp * 8 + 2 * t + i) * 2] = best[i];
-            merge_stat[(warp * 8 + 2 * t + i) * 2 + 1] = denom[i];
+            for (int n = 0; n < D / 16; ++n) {
+                mine[n * 16 + g] = o[n][i];
+                mine[n * 16 + g + 8] = o[n][2 + i];
+            }
+            if (g == 0) {
+                merge_stat[(warp * 8 + head) * 2] = best[i];
+                merge_stat[(warp * 8 + head) * 2 + 1] = denom[i];
+            }
         }
     }
     __syncthreads();
-    // Per head: the block's maximum and denominator and each warp's weight in the merge (a
-    // thread per (head, warp) pair would do; one per head keeps the order of the sums fixed).
+    // Per head: the block's maximum and denominator and each warp's weight in the merge, by the
+    // lanes of one warp (lane = 8 * warp of the partial + head; the sums run through a fixed tree
+    // of shuffles, so their order does not depend on timing).
     float* merge_weight = merge_stat + 4 * 8 * 2;                        // [4][8], then [8][2]: maximum, denominator
-    if (threadIdx.x < group) {
-        const int r = threadIdx.x;
-        float top = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) top = fmaxf(top, merge_stat[(w * 8 + r) * 2]);
-        float total = 0.f;
+    if (warp == 0) {
+        const int source = lane >> 3, r = lane & 7;
+        const bool real = r < group;
+        const float m = real ? merge_stat[(source * 8 + r) * 2] : -INFINITY;
+        const float d = real ? merge_stat[(source * 8 + r) * 2 + 1] : 0.f;
+        float top = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 16));
+        const float factor = m == -INFINITY ? 0.f : exp2f(m - top);
+        float total = d * factor;
+        total += __shfl_xor_sync(0xffffffffu, total, 8);
+        total += __shfl_xor_sync(0xffffffffu, total, 16);
+        merge_weight[source * 8 + r] = factor;
+        if (source == 0) {
+            merge_weight[32 + r * 2] = top;
+            merge_weight[32 + r * 2 + 1] = total;
+        }
+        if (CLUSTER && a.splits > 1) {                                   // every block of the cluster needs them
+            for (int base = 0; base < a.splits * group; base += 32) {    // the whole warp shuffles together
+                const int i = base + lane;
+                const bool sends = i < a.splits * group;
+                const int target = sends ? i / group : 0, head = sends ? i - target * group : 0;
+                const float head_top = __shfl_sync(0xffffffffu, top, head), head_total = __shfl_sync(0xffffffffu, total, head);
+                if (sends)
+                    *reinterpret_cast<float2*>(cluster.map_shared_rank(recv_stat, target) + (split * 8 + head) * 2) =
+                        make_float2(head_top, head_total);
+            }
+        }
+    }
+    __syncthreads();
+    // Four elements a thread: the weighted sum of the four warps' partial results, then to where
+    // the splits are merged. A cluster's blocks share the output elements in pieces of `share`
+    // elements (a multiple of four), and each sends its partial values to the block that merges
+    // them (distributed shared memory, 16 bytes a store).
+    const int share = CLUSTER ? ((group * D + a.splits - 1) / a.splits + 3) & ~3 : 0;
+    for (int item = threadIdx.x * 4; item < group * D; item += THREADS * 4) {
+        const int r = item / D, c = item - r * D;
+        float4 value = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float m = merge_stat[(w * 8 + r) * 2];
-            const float factor = m == -INFINITY ? 0.f : exp2f(m - top);
-            total += merge_stat[(w * 8 + r) * 2 + 1] * factor;
-            merge_weight[w * 8 + r] = factor;
+            const float4 part = *reinterpret_cast<const float4*>(merge_out + (w * 8 + r) * MP + c);
+            const float weight = merge_weight[w * 8 + r];
+            value.x += part.x * weight; value.y += part.y * weight; value.z += part.z * weight; value.w += part.w * weight;
         }
-        merge_weight[32 + r * 2] = top;
-        merge_weight[32 + r * 2 + 1] = total;
-        if (CLUSTER && a.splits > 1)                                     // every block of the cluster needs them
-            for (int d = 0; d < a.splits; ++d) {
-                float* stat = cluster.map_shared_rank(recv_stat, d) + (split * 8 + r) * 2;
-                stat[0] = top;
-                stat[1] = total;
-            }
-    }
-    __syncthreads();
-    for (int item = threadIdx.x; item < group * D; item += THREADS) {
-        const int r = item / D, c = item - r * D;
-        const float top = merge_weight[32 + r * 2], total = merge_weight[32 + r * 2 + 1];
-        float value = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) value += merge_out[(w * 8 + r) * D + c] * merge_weight[w * 8 + r];
         const int head = head0 + r;
         if (a.splits == 1) {
-            a.out[(long long)row * a.ldo + (long long)head * D + c] =
-                from_float<bf16>(total > 0.f ? value / total : 0.f);
+            const float total = merge_weight[32 + r * 2 + 1];
+            const float scale = total > 0.f ? 1.0f / total : 0.f;
+            bf16* out = a.out + (long long)row * a.ldo + (long long)head * D + c;
+            *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(value.x * scale, value.y * scale);
+            *reinterpret_cast<__nv_bfloat162*>(out + 2) = __floats2bfloat162_rn(value.z * scale, value.w * scale);
         } else if (CLUSTER) {
-            // The cluster's blocks share the output elements; this one sends each element of its
-            // partial result to the block that merges it (distributed shared memory).
-            const int share = (group * D + a.splits - 1) / a.splits;
             const int target = item / share;
-            cluster.map_shared_rank(recv_out, target)[split * share + item - target * share] = value;
+            *reinterpret_cast<float4*>(cluster.map_shared_rank(recv_out, target) + split * share + item - target * share) = value;
         } else {
             const long long where = ((long long)row * a.heads + head) * a.splits + split;
-            a.partial_out[where * D + c] = value;
+            *reinterpret_cast<float4*>(a.partial_out + where * D + c) = value;
             if (c == 0) {
-                a.partial_stat[where * 2] = top;
-                a.partial_stat[where * 2 + 1] = total;
+                a.partial_stat[where * 2] = merge_weight[32 + r * 2];
+                a.partial_stat[where * 2 + 1] = merge_weight[32 + r * 2 + 1];
             }
         }
     }
@@ -977,21 +1012,24 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
         // may leave as soon as it has written its share.
         cluster.sync();
         const int splits = a.splits;                   // == the cluster's size, <= 8
-        const int share = (group * D + splits - 1) / splits;
         const int begin = split * share, count = min(group * D, begin + share) - begin;
-        for (int i = threadIdx.x; i < count; i += THREADS) {
+        for (int i = threadIdx.x * 4; i < count; i += THREADS * 4) {
             const int r = (begin + i) / D, c = begin + i - r * D;
             float top = -INFINITY;
             for (int sp = 0; sp < splits; ++sp) top = fmaxf(top, recv_stat[(sp * 8 + r) * 2]);
-            float total = 0.f, value = 0.f;
+            float total = 0.f;
+            float4 value = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int sp = 0; sp < splits; ++sp) {
                 const float m = recv_stat[(sp * 8 + r) * 2];
                 const float factor = m == -INFINITY ? 0.f : exp2f(m - top);
                 total += recv_stat[(sp * 8 + r) * 2 + 1] * factor;
-                value += recv_out[sp * share + i] * factor;
+                const float4 part = *reinterpret_cast<const float4*>(recv_out + sp * share + i);
+                value.x += part.x * factor; value.y += part.y * factor; value.z += part.z * factor; value.w += part.w * factor;
             }
-            a.out[(long long)row * a.ldo + (long long)(head0 + r) * D + c] =
-                from_float<bf16>(total > 0.f ? value / total : 0.f);
+            const float scale = total > 0.f ? 1.0f / total : 0.f;
+            bf16* out = a.out + (long long)row * a.ldo + (long long)(head0 + r) * D + c;
+            *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(value.x * scale, value.y * scale);
+            *reinterpret_cast<__nv_bfloat162*>(out + 2) = __floats2bfloat162_rn(value.z * scale, value.w * scale);
         }
         return;
     }

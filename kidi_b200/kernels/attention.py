@@ -158,7 +158,7 @@ def blocks_per_sm(head_dim: int = 128, ring: bool = False) -> int:
     rows padded by 8 elements, or with `ring` three unpadded ones), what a cluster's blocks send
     each other and a kilobyte of the system's; at most four by registers. Three at head width
     128, four with the ring."""
-    received = (8 * head_dim + 8 + 128) * 4
+    received = (8 * head_dim + 32 + 128) * 4 + 128
     if ring:
         block = 1024 + (3 * 64 * head_dim + 8 * (head_dim + 8)) * 2 + received + 1024
     else:
@@ -182,7 +182,7 @@ def decode_ring(rows: int, kv_heads: int, device: torch.device, head_dim: int) -
 # What a block spends beside its tiles (launch, tables, query, merge of the splits), in tile
 # times, fitted to kernel times measured on a B200 (batch 1 to 64, 300 to 16,000 tokens): less
 # when the splits merge inside a thread-block cluster than through a workspace.
-FIXED_COST_TILES = 6.5
+FIXED_COST_TILES = 14.0
 FIXED_COST_TILES_CLUSTER = 3.5
 
 
