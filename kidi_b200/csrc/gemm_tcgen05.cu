@@ -8,12 +8,16 @@
 // memory descriptors name; a ring of STAGES tiles is kept in flight with mbarriers.
 // One thread issues the copies, one thread issues tcgen05.mma (four k=16 steps per
 // tile, the descriptor's start address advanced by 32 bytes inside the swizzle atom),
-// and four warps read the accumulator back with tcgen05.ld for the epilogue.
+// and four warps read the accumulator back with tcgen05.ld for the epilogue. Blocks are
+// persistent (one per SM, each walking its share of the tiles) and the accumulator is
+// double-buffered in tensor memory, so that the epilogue of one tile runs under the
+// products of the next and the ring of operand stages never drains between tiles.
 //
-// With few tokens the product is bound by reading W once: a block then takes only a
-// slice of K (split-K) so that every SM streams weights; blocks write their partial
-// tiles to a workspace and the last one to arrive for a tile (an atomic counter) adds
-// them in slice order, so the result does not depend on timing. Epilogues: store
+// The k-blocks of all tiles are dealt out evenly over the blocks (see the kernel): with few
+// tokens, where the product is bound by reading W once, that is split-K and every SM streams
+// weights; with many it fills the last round of blocks. Parts of tiles meet in a workspace and
+// the last block to arrive for a tile (an atomic counter) adds them in their order along k,
+// so the result does not depend on timing. Epilogues: store
 // (bfloat16 or float32), or the SiLU gate of a fused [gate | up] projection, for which a
 // tile is 64 gate rows and the 64 matching up rows.
 //
@@ -21,6 +25,7 @@
 // code in `error`, waits (bounded) for its copies in flight, frees its tensor memory
 // and returns.
 #include <cuda.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -41,6 +46,9 @@ __device__ __forceinline__ void mbarrier_init(unsigned long long* bar, int count
 }
 __device__ __forceinline__ void mbarrier_expect_tx(unsigned long long* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarrier_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbarrier_try_wait(unsigned long long* bar, unsigned parity) {
     unsigned done;
@@ -68,6 +76,16 @@ __device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, 
         :
         : "r"(smem_u32(smem)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
+}
+
+// A tile of shared memory to global memory through a tensor map (clipped at the tensor's edges);
+// the copies of a thread form groups that it can wait for.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :
+                 : "l"((unsigned long long)map), "r"(smem_u32(smem)), "r"(x), "r"(y)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
 // Shared memory descriptor of a K-major tile with the 128-byte swizzle: rows are 128
@@ -115,48 +133,80 @@ __device__ __forceinline__ void tmem_load_16(unsigned address, float (&v)[16]) {
 
 struct Params {
     void* y;               // [tokens, ldy]
-    float* workspace;      // [units][BM][BN] partial tiles (split-K only)
-    int* counters;         // [feature tiles * token tiles], zero between calls (the kernel leaves them zero)
+    float* workspace;      // [2 * blocks][BM][BN] partial tiles
+    int* counters;         // [blocks], zero between calls (the kernel leaves them zero)
     int* error;            // set to a non-zero code when a bounded wait ran out
     const float* bias;     // [features] added to every token's row, or null (not with the gate)
     long long ldy;
     int tokens, features;  // features: width of y (for the gated form the weight has 2 * features rows)
-    int k_blocks;          // ceil(K / 64)
-    int splits;            // blocks that share one tile's K range
-    int feature_tiles;
+    int k_blocks;          // ceil(K / 64): the k-blocks of one tile
+    int token_tiles;
+    long long tiles;
+    int rounds;            // whole tiles a block takes for itself: tiles b, b + blocks, ... (while there are)
+    long long tail_first;  // the first tile of the tail
+    int share, extra;      // of the tail's k-blocks a block takes `share`, the first `extra` blocks one more
+    int staged;            // results leave through shared memory and TMA stores (bfloat16 y, 16-byte aligned rows)
 };
 
+// Tiles are numbered so that the blocks at work at one time share few weight tiles and few token
+// tiles (see `locate`). With a tile for every block, block b takes whole tiles b,
+// b + blocks, ... and writes their results to y. With fewer tiles than blocks (few tokens: the
+// product is bound by reading the weights once) the tiles' k-blocks form one line, tile after
+// tile, of which every block takes an equal, contiguous piece; the blocks being a multiple of
+// the tiles, that is split-K. A piece's parts of tiles go to the workspace; the block that
+// brings a tile's last part adds all parts in their order along k, so the result does not
+// depend on timing.
+// A block keeps its ring of operand stages full across the borders of tiles, and the accumulator
+// is double-buffered in tensor memory (2 x BN columns): while the four epilogue warps read one
+// piece of work out, the tensor core is at the next.
 template <int BN, int STAGES, bool GATED, typename TY>
-__global__ void __launch_bounds__(THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, Params p) {
+__global__ void __launch_bounds__(THREADS, BN <= 64 ? 2 : 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const __grid_constant__ CUtensorMap map_y, Params p) {
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int TMEM_COLUMNS = BN < 32 ? 32 : BN;
+    constexpr int BUFFER_COLUMNS = BN < 32 ? 32 : BN;      // columns of one accumulator
+    constexpr int TMEM_COLUMNS = 2 * BUFFER_COLUMNS;        // 64 .. 512, a power of two
     constexpr int SPAN = GATED ? 64 : BM;                  // output features per tile
     extern __shared__ unsigned char raw[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
-    __shared__ unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
+    // The gated epilogue passes the up rows of a 16-column chunk between warps (64 x 17 floats).
+    float* exchange = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES);
+    // Results on their way out (p.staged): two buffers of 16 tokens x SPAN features, which TMA stores
+    // write to y in whole lines (a thread holds one feature of 16 tokens: stored directly, every
+    // token's 32 features of a warp would be a 64-byte piece of its own).
+    bf16* staging = reinterpret_cast<bf16*>(tiles + (size_t)STAGES * STAGE_BYTES + 64 * 17 * sizeof(float));
+    __shared__ unsigned long long full_bar[STAGES], empty_bar[STAGES], ready_bar[2], drained_bar[2];
     __shared__ unsigned tmem_base_slot;
     __shared__ int gave_up, is_last;
-    // The gated epilogue passes the up rows of a 16-column chunk between warps (64 x 17
-    // floats): in the first stage's tile, which is free once the accumulator is complete (a
-    // buffer of its own would leave room for one block per SM instead of two).
-    float* exchange = reinterpret_cast<float*>(tiles);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int feature_tile = blockIdx.x % p.feature_tiles, split = blockIdx.x / p.feature_tiles;
-    const int token_tile = blockIdx.y;
-    const int f0 = feature_tile * SPAN, t0 = token_tile * BN;
-    // This block's slice of the k-blocks: slices differ by at most one block.
-    const int base = p.k_blocks / p.splits, extra = p.k_blocks % p.splits;
-    const int kb_first = split * base + min(split, extra);
-    const int kb_count = base + (split < extra ? 1 : 0);
+    // Where block c's piece of the line begins, and which block holds k-block g of the line.
+    auto begin_of = [&](long long c) -> long long { return c * p.share + (c < p.extra ? c : p.extra); };   // in the tail's line
+    auto block_of = [&](long long g) -> int {
+        const long long heavy = (long long)p.extra * (p.share + 1);
+        return g < heavy ? (int)(g / (p.share + 1)) : (int)(p.extra + (g - heavy) / p.share);
+    };
+    const long long piece_begin = begin_of(blockIdx.x), piece_end = begin_of(blockIdx.x + 1);
+    // Tiles are numbered in columns of eight token tiles: within a column token tile first, then
+    // feature tile (the blocks at work at one time share few weight tiles and eight token tiles,
+    // however long the prompt), column after column.
+    const int feature_tiles = (int)(p.tiles / p.token_tiles);
+    auto locate = [&](long long tile, int& token_tile, int& feature_tile) {
+        const long long column = tile / (8LL * feature_tiles), within = tile - column * 8 * feature_tiles;
+        const int wide = min(8, p.token_tiles - (int)column * 8);
+        token_tile = (int)column * 8 + (int)(within % wide);
+        feature_tile = (int)(within / wide);
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbarrier_init(&full_bar[s], 1);
             mbarrier_init(&empty_bar[s], 1);
         }
-        mbarrier_init(&done_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbarrier_init(&ready_bar[b], 1);       // the tensor core has finished an accumulator
+            mbarrier_init(&drained_bar[b], 128);   // every epilogue thread has read it out
+        }
         gave_up = 0;
         is_last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -174,24 +224,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------ producer
-        int issued = 0;
-        for (int i = 0; i < kb_count; ++i) {
-            const int s = i % STAGES;
-            if (i >= STAGES && !mbarrier_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag)) {
-                if (!*abort_flag) { *abort_flag = 1; atomicExch(p.error, 1); }
-                break;
+        int issued = 0;                                   // stages filled so far
+        auto load = [&](long long tile, int kb_first, int kb_count) {
+            int token_tile, feature_tile;
+            locate(tile, token_tile, feature_tile);
+            const int f0 = feature_tile * SPAN, t0 = token_tile * BN;
+            for (int i = 0; i < kb_count; ++i, ++issued) {
+                const int s = issued % STAGES;
+                if (issued >= STAGES && !mbarrier_wait(&empty_bar[s], ((issued / STAGES) - 1) & 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.error, 1); }
+                    return;
+                }
+                unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
+                mbarrier_expect_tx(&full_bar[s], STAGE_BYTES);
+                const int k = (kb_first + i) * BK;
+                if (GATED) {
+                    tma_load_2d(stage, &map_w, &full_bar[s], k, f0);                            // 64 gate rows
+                    tma_load_2d(stage + A_BYTES / 2, &map_w, &full_bar[s], k, p.features + f0);  // 64 up rows
+                } else {
+                    tma_load_2d(stage, &map_w, &full_bar[s], k, f0);
+                }
+                tma_load_2d(stage + A_BYTES, &map_x, &full_bar[s], k, t0);
             }
-            unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
-            mbarrier_expect_tx(&full_bar[s], STAGE_BYTES);
-            const int k = (kb_first + i) * BK;
-            if (GATED) {
-                tma_load_2d(stage, &map_w, &full_bar[s], k, f0);                            // 64 gate rows
-                tma_load_2d(stage + A_BYTES / 2, &map_w, &full_bar[s], k, p.features + f0);  // 64 up rows
-            } else {
-                tma_load_2d(stage, &map_w, &full_bar[s], k, f0);
-            }
-            tma_load_2d(stage + A_BYTES, &map_x, &full_bar[s], k, t0);
-            ++issued;
+        };
+        for (int round = 0; round < p.rounds && !*abort_flag; ++round)
+            if (blockIdx.x + (long long)round * gridDim.x < p.tail_first)
+                load(blockIdx.x + (long long)round * gridDim.x, 0, p.k_blocks);
+        for (long long g = piece_begin; g < piece_end && !*abort_flag;) {
+            const long long tile = g / p.k_blocks;
+            const int kb_first = (int)(g - tile * p.k_blocks);
+            const int kb_count = (int)min((long long)(p.k_blocks - kb_first), piece_end - g);
+            load(p.tail_first + tile, kb_first, kb_count);
+            g += kb_count;
         }
         if (*abort_flag) {  // let the copies in flight land before the block leaves
             for (int i = max(0, issued - STAGES); i < issued; ++i)
@@ -201,99 +265,164 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else if (warp == 1 && lane == 0) {
         // -------------------------------------------------------------- issuer
         constexpr unsigned idesc = make_instr_desc(BN);
-        for (int i = 0; i < kb_count; ++i) {
-            const int s = i % STAGES;
-            if (!mbarrier_wait(&full_bar[s], (i / STAGES) & 1, abort_flag)) {
-                if (!*abort_flag) { *abort_flag = 1; atomicExch(p.error, 2); }
-                break;
+        int consumed = 0, done = 0;                        // stages read, accumulators finished
+        auto multiply = [&](int kb_count) {
+            const int buffer = done & 1;
+            // The accumulator's last reader (two pieces of work ago) must have read it out.
+            if (done >= 2 && !mbarrier_wait(&drained_bar[buffer], ((done >> 1) - 1) & 1, abort_flag)) {
+                if (!*abort_flag) { *abort_flag = 1; atomicExch(p.error, 4); }
+                return;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
-            const unsigned long long desc_a = make_smem_desc(stage), desc_b = make_smem_desc(stage + A_BYTES);
+            const unsigned accumulator = tmem_base + buffer * BUFFER_COLUMNS;
+            for (int i = 0; i < kb_count; ++i, ++consumed) {
+                const int s = consumed % STAGES;
+                if (!mbarrier_wait(&full_bar[s], (consumed / STAGES) & 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.error, 2); }
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
+                const unsigned long long desc_a = make_smem_desc(stage), desc_b = make_smem_desc(stage + A_BYTES);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further inside the swizzle span: +2 in 16-byte units
-                umma_bf16(tmem_base, desc_a + 2 * k, desc_b + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-            umma_commit(&empty_bar[s]);  // arrives when these instructions have read the stage
+                for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further inside the swizzle span: +2 in 16-byte units
+                    umma_bf16(accumulator, desc_a + 2 * k, desc_b + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty_bar[s]);  // arrives when these instructions have read the stage
+            }
+            umma_commit(&ready_bar[buffer]);  // arrives when the accumulator is complete
+            ++done;
+        };
+        for (int round = 0; round < p.rounds && !*abort_flag; ++round)
+            if (blockIdx.x + (long long)round * gridDim.x < p.tail_first) multiply(p.k_blocks);
+        for (long long g = piece_begin; g < piece_end && !*abort_flag;) {
+            const int kb_first = (int)(g % p.k_blocks);
+            const int kb_count = (int)min((long long)(p.k_blocks - kb_first), piece_end - g);
+            multiply(kb_count);
+            g += kb_count;
         }
-        umma_commit(&done_bar);          // arrives when the accumulator is complete
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;                     // TMEM lanes 32 * quarter .. + 31
         const int row = quarter * 32 + lane;              // row of the tile = TMEM lane
-        bool ok = kb_count == 0 || mbarrier_wait(&done_bar, 0, abort_flag);
-        if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(p.error, 3); }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const long long tile_index = (long long)token_tile * p.feature_tiles + feature_tile;
-        bool reduce = false;
-        if (p.splits > 1) {
-            // Partial tile to the workspace; the last block to arrive adds all of them.
-            float* mine = p.workspace + ((tile_index * p.splits + split) * BM + row) * BN;
+        int done = 0, staged_chunks = 0;
+        // `tail_tile` < 0: a whole tile of this block's own; else the tile's number within the tail, of
+        // which this block brings k-blocks kb_first .. kb_first + kb_count - 1.
+        auto finish = [&](long long tile, long long tail_tile, int kb_first, int kb_count) {
+            int token_tile, feature_tile;
+            locate(tile, token_tile, feature_tile);
+            const int f0 = feature_tile * SPAN, t0 = token_tile * BN;
+            const int buffer = done & 1;
+            const unsigned accumulator = tmem_base + buffer * BUFFER_COLUMNS + ((unsigned)(quarter * 32) << 16);
+            bool ok = !*abort_flag && mbarrier_wait(&ready_bar[buffer], (done >> 1) & 1, abort_flag);
+            if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(p.error, 3); }
+            ++done;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool whole = kb_count == p.k_blocks;    // the tile is this block's alone
+            // A shared tile: the blocks that hold its first and last k-block, the parts between them.
+            const int first_block = whole ? 0 : block_of(tail_tile * p.k_blocks);
+            const int parts = whole ? 1 : block_of((tail_tile + 1) * p.k_blocks - 1) - first_block + 1;
+            bool reduce = false;
+            if (!whole) {
+                // This part to the workspace (a block has at most two parts: the one its piece begins
+                // with and the one it ends with), column by column so that a warp writes whole lines;
+                // the block that brings the last part adds all of them.
+                const long long slot = 2LL * blockIdx.x + (kb_first > 0 || piece_begin == tail_tile * p.k_blocks ? 0 : 1);
+                float* mine = p.workspace + slot * BM * BN + row;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                float v[16];
-                if (ok && kb_count > 0) tmem_load_16(tmem_base + ((unsigned)(quarter * 32) << 16) + c, v);
-                else
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
-#pragma unroll
-                for (int i = 0; i < 16; i += 4)
-                    *reinterpret_cast<float4*>(mine + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) is_last = atomicAdd(p.counters + tile_index, 1) == p.splits - 1;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            reduce = is_last != 0;
-            if (reduce) __threadfence();
-        }
-        if (p.splits == 1 || reduce) {
-            TY* y = (TY*)p.y;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                float v[16];
-                if (p.splits == 1) {
-                    if (ok && kb_count > 0) tmem_load_16(tmem_base + ((unsigned)(quarter * 32) << 16) + c, v);
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    if (ok) tmem_load_16(accumulator + c, v);
                     else
 #pragma unroll
                         for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                } else {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                    for (int s = 0; s < p.splits; ++s) {  // slice order: the sum does not depend on timing
-                        const float* part = p.workspace + ((tile_index * p.splits + s) * BM + row) * BN + c;
+                    for (int i = 0; i < 16; ++i) mine[(long long)(c + i) * BM] = v[i];
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbarrier_arrive(&drained_bar[buffer]);       // the tensor core may have the accumulator back
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) is_last = atomicAdd(p.counters + first_block, 1) == parts - 1;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                reduce = is_last != 0;
+                if (reduce) __threadfence();
+            }
+            if (whole || reduce) {
+                TY* y = (TY*)p.y;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    if (whole) {
+                        if (ok) tmem_load_16(accumulator + c, v);
+                        else
 #pragma unroll
-                        for (int i = 0; i < 16; i += 4) {
-                            const float4 q = __ldcg(reinterpret_cast<const float4*>(part + i));
-                            v[i] += q.x; v[i + 1] += q.y; v[i + 2] += q.z; v[i + 3] += q.w;
+                            for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                        for (int part = 0; part < parts; ++part) {  // in their order along k: the sum does not depend on timing
+                            const long long holder = first_block + part;
+                            const long long slot = 2 * holder + (begin_of(holder) >= tail_tile * p.k_blocks ? 0 : 1);
+                            const float* from = p.workspace + slot * BM * BN + (long long)c * BM + row;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] += __ldcg(from + i * BM);
                         }
                     }
-                }
-                if (GATED) {
-                    // Rows 64..127 hold the up projection of the features in rows 0..63.
-                    if (row >= 64)
+                    bool mine = f0 + row < p.features;    // this thread has results of this chunk
+                    if (GATED) {
+                        // Rows 64..127 hold the up projection of the features in rows 0..63.
+                        if (row >= 64)
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) exchange[(row - 64) * 17 + i] = v[i];
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (row < 64 && f0 + row < p.features)
+                            for (int i = 0; i < 16; ++i) exchange[(row - 64) * 17 + i] = v[i];
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        mine = mine && row < 64;
+                        if (row < 64)
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * exchange[row * 17 + i];
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                    } else if (p.bias && mine) {
+                        const float shift = p.bias[f0 + row];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] += shift;
+                    }
+                    if (sizeof(TY) == 2 && p.staged) {
+                        bf16* out = staging + (staged_chunks & 1) * (16 * SPAN);
+                        // The copy that read this buffer two chunks ago must be through with it.
+                        if (threadIdx.x == 64 && staged_chunks >= 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (row < SPAN)
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) out[i * SPAN + row] = __float2bfloat16_rn(v[i]);
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the copy reads what these threads wrote
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (threadIdx.x == 64) tma_store_2d(&map_y, out, f0, t0 + c);
+                        ++staged_chunks;
+                    } else if (mine) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             const int token = t0 + c + i;
-                            const float gate = v[i], up = exchange[row * 17 + i];
-                            if (token < p.tokens)
-                                y[token * p.ldy + f0 + row] = from_float<TY>(gate / (1.0f + expf(-gate)) * up);
+                            if (token < p.tokens) y[token * p.ldy + f0 + row] = from_float<TY>(v[i]);
                         }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                } else if (f0 + row < p.features) {
-                    const float shift = p.bias ? p.bias[f0 + row] : 0.f;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int token = t0 + c + i;
-                        if (token < p.tokens) y[token * p.ldy + f0 + row] = from_float<TY>(v[i] + shift);
                     }
                 }
+                if (whole) {
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbarrier_arrive(&drained_bar[buffer]);
+                }
+                if (reduce && threadIdx.x == 64) p.counters[first_block] = 0;  // ready for the next call
             }
-            if (reduce && threadIdx.x == 64) p.counters[tile_index] = 0;  // ready for the next call
+        };
+        for (int round = 0; round < p.rounds; ++round)
+            if (blockIdx.x + (long long)round * gridDim.x < p.tail_first)
+                finish(blockIdx.x + (long long)round * gridDim.x, -1, 0, p.k_blocks);
+        for (long long g = piece_begin; g < piece_end;) {
+            const long long tail_tile = g / p.k_blocks;
+            const int kb_first = (int)(g - tail_tile * p.k_blocks);
+            const int kb_count = (int)min((long long)(p.k_blocks - kb_first), piece_end - g);
+            finish(p.tail_first + tail_tile, tail_tile, kb_first, kb_count);
+            g += kb_count;
         }
+        if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the last stores have left
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -333,9 +462,40 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
     return status == CUDA_SUCCESS ? 0 : 1000 + (int)status;
 }
 
+int sm_count_of_current_device() {
+    static int cached[64] = {0};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 1;
+    if (!cached[device]) {
+        int count = 0;
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count < 1) return 1;
+        cached[device] = count;
+    }
+    return cached[device];
+}
+
+// A map over y [tokens, features] (bfloat16, leading dimension ld) for stores of 16 tokens x `span` features.
+int make_store_map(CUtensorMap* map, void* base, long long tokens, long long features, long long ld, int span) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return KIDI_REFUSED_SIZE;
+    const cuuint64_t dims[2] = {(cuuint64_t)features, (cuuint64_t)tokens};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)span, 16};
+    const cuuint32_t steps[2] = {1, 1};
+    CUresult status = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, steps,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return status == CUDA_SUCCESS ? 0 : 1000 + (int)status;
+}
+
 template <int BN, int STAGES, bool GATED, typename TY>
-int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, int token_tiles, cudaStream_t stream) {
-    constexpr size_t shared = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const CUtensorMap& map_y, const Params& p, int blocks,
+           cudaStream_t stream) {
+    // The stages, a kilobyte to align them, the gated epilogue's exchange buffer and two buffers of
+    // results on their way out.
+    constexpr size_t shared = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 64 * 17 * sizeof(float) +
+                              2 * 16 * BM * sizeof(bf16);
+    static_assert(shared <= (BN <= 64 ? 113 : 227) * 1024, "the stages fit an SM's shared memory (twice for small tiles)");
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, GATED, TY>;
     static bool configured = false;
     if (!configured) {
@@ -343,20 +503,19 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, 
         if (status != cudaSuccess) return (int)status;
         configured = true;
     }
-    dim3 grid(p.feature_tiles * p.splits, token_tiles);
-    kernel<<<grid, THREADS, shared, stream>>>(map_w, map_x, p);
+    kernel<<<blocks, THREADS, shared, stream>>>(map_w, map_x, map_y, p);
     return kidi_launch_status();
 }
 
 template <bool GATED, typename TY>
-int by_tokens(int bn, const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, int token_tiles,
-              cudaStream_t stream) {
-    switch (bn) {
-        case 16: return launch<16, 6, GATED, TY>(map_w, map_x, p, token_tiles, stream);
-        case 32: return launch<32, 5, GATED, TY>(map_w, map_x, p, token_tiles, stream);
-        case 64: return launch<64, 4, GATED, TY>(map_w, map_x, p, token_tiles, stream);
-        case 128: return launch<128, 6, GATED, TY>(map_w, map_x, p, token_tiles, stream);
-        case 256: return launch<256, 4, GATED, TY>(map_w, map_x, p, token_tiles, stream);
+int by_tokens(int bn, const CUtensorMap& map_w, const CUtensorMap& map_x, const CUtensorMap& map_y, const Params& p,
+              int blocks, cudaStream_t stream) {
+    switch (bn) {   // stages of 16 KB of weights + 128 bytes a token: two blocks an SM up to 64 tokens, one above
+        case 16: return launch<16, 5, GATED, TY>(map_w, map_x, map_y, p, blocks, stream);
+        case 32: return launch<32, 4, GATED, TY>(map_w, map_x, map_y, p, blocks, stream);
+        case 64: return launch<64, 4, GATED, TY>(map_w, map_x, map_y, p, blocks, stream);
+        case 128: return launch<128, 6, GATED, TY>(map_w, map_x, map_y, p, blocks, stream);
+        case 256: return launch<256, 4, GATED, TY>(map_w, map_x, map_y, p, blocks, stream);
     }
     return KIDI_REFUSED_SIZE;
 }
@@ -367,22 +526,36 @@ KIDI_API int kidi_gemm_tcgen05_token_tile(int tokens) {
     return tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : tokens <= 128 ? 128 : 256;
 }
 
-// Floats of workspace a call needs (0 without split-K) and the number of counters.
-KIDI_API long long kidi_gemm_tcgen05_workspace(int tokens, int features, int splits, int gated) {
+// How many blocks a call launches: as many as are resident at once (two per SM up to 64 tokens, one
+// above), or, when there are fewer tiles than that, a multiple of the tiles (so that no block's
+// piece lies in two tiles): `splits` > 0 asks for that many blocks per tile, 0 for as many as fit.
+KIDI_API int kidi_gemm_tcgen05_blocks(int tokens, int features, int K, int gated, int splits) {
     const int bn = kidi_gemm_tcgen05_token_tile(tokens);
     const long long tiles = (long long)((features + (gated ? 64 : BM) - 1) / (gated ? 64 : BM)) * ((tokens + bn - 1) / bn);
-    return splits > 1 ? tiles * splits * BM * bn : 0;
+    const int k_blocks = (K + BK - 1) / BK;
+    const long long resident = (long long)sm_count_of_current_device() * (bn <= 64 ? 2 : 1);
+    if (tiles >= resident) return (int)resident;
+    long long per_tile = resident / tiles;
+    if (splits > 0 && splits < per_tile) per_tile = splits;
+    if (per_tile > k_blocks) per_tile = k_blocks;
+    return (int)(tiles * (per_tile < 1 ? 1 : per_tile));
+}
+
+// Floats of workspace a call needs (two partial tiles a block) and, in counters, its number of blocks.
+KIDI_API long long kidi_gemm_tcgen05_workspace(int tokens, int features, int K, int gated, int splits) {
+    const int bn = kidi_gemm_tcgen05_token_tile(tokens);
+    return 2LL * kidi_gemm_tcgen05_blocks(tokens, features, K, gated, splits) * BM * bn;
 }
 
 // x [tokens, K] and w [features (2 * features when gated), K] bfloat16, rows 16-byte
-// aligned; y [tokens, features] bfloat16 or float32. `workspace`, `counters` (zeroed
-// once by the caller; the kernel leaves them zero) and `error` are the caller's. `bias`
-// (float32 [features], or null) is added to every row.
+// aligned; y [tokens, features] bfloat16 or float32. `workspace` (kidi_gemm_tcgen05_workspace
+// floats), `counters` (one per block; zeroed once by the caller; the kernel leaves them zero) and
+// `error` are the caller's. `bias` (float32 [features], or null) is added to every row.
 KIDI_API int kidi_gemm_tcgen05(const void* x, const void* w, void* y, int y_dtype, int tokens, int features, int K,
                                long long ldx, long long ldw, long long ldy, int gated, int splits, float* workspace,
                                int* counters, int* error, const float* bias, cudaStream_t stream) {
     if (tokens <= 0 || features <= 0) return 0;
-    if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || splits < 1)
+    if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || splits < 0)
         return KIDI_REFUSED_SIZE;
     const int bn = kidi_gemm_tcgen05_token_tile(tokens);
     const int span = gated ? 64 : BM;
@@ -396,23 +569,39 @@ KIDI_API int kidi_gemm_tcgen05(const void* x, const void* w, void* y, int y_dtyp
     p.tokens = tokens;
     p.features = features;
     p.k_blocks = (K + BK - 1) / BK;
-    p.splits = splits > p.k_blocks ? p.k_blocks : splits;
-    p.feature_tiles = (features + span - 1) / span;
-    if (p.splits > 1 && (!workspace || !counters)) return KIDI_REFUSED_SIZE;
-    if (!error) return KIDI_REFUSED_SIZE;
-    const int token_tiles = (tokens + bn - 1) / bn;
-    if (token_tiles > 65535) return KIDI_REFUSED_SIZE;
+    p.token_tiles = (tokens + bn - 1) / bn;
+    const long long tiles = (long long)((features + span - 1) / span) * p.token_tiles;
+    const int blocks = kidi_gemm_tcgen05_blocks(tokens, features, K, gated, splits);
+    if (tiles / blocks > 0x7fffffffLL) return KIDI_REFUSED_SIZE;
+    p.tiles = tiles;
+    // A tile for every block: whole tiles only, block b takes b, b + blocks, ... (sharing the tiles of
+    // the last, partly filled round out in k-blocks was measured slower: the parts' trip through the
+    // workspace costs more than the idle SMs). Fewer tiles than blocks: all of it is tail.
+    p.rounds = tiles >= blocks ? (int)((tiles + blocks - 1) / blocks) : 0;
+    p.tail_first = tiles >= blocks ? tiles : 0;
+    const long long tail = (tiles - p.tail_first) * p.k_blocks;   // dealt out in k-blocks
+    p.share = (int)(tail / blocks);
+    p.extra = (int)(tail % blocks);
+    if (!workspace || !counters || !error) return KIDI_REFUSED_SIZE;
     CUtensorMap map_w, map_x;
     int status = make_map(&map_w, w, gated ? 2LL * features : features, K, ldw, gated ? 64 : BM);
     if (status) return status;
     status = make_map(&map_x, x, tokens, K, ldx, bn);
     if (status) return status;
+    // bfloat16 results whose rows 16-byte copies can write leave through shared memory and TMA stores.
+    CUtensorMap map_y;
+    memset(&map_y, 0, sizeof(map_y));
+    p.staged = y_dtype == KIDI_BF16 && !(ldy & 7) && !((uintptr_t)y & 15);
+    if (p.staged) {
+        status = make_store_map(&map_y, y, tokens, features, ldy, span);
+        if (status) return status;
+    }
     if (gated) {
         if (y_dtype != KIDI_BF16) return KIDI_REFUSED_DTYPE;
         if (bias) return KIDI_REFUSED_SIZE;
-        return by_tokens<true, bf16>(bn, map_w, map_x, p, token_tiles, stream);
+        return by_tokens<true, bf16>(bn, map_w, map_x, map_y, p, blocks, stream);
     }
-    if (y_dtype == KIDI_BF16) return by_tokens<false, bf16>(bn, map_w, map_x, p, token_tiles, stream);
-    if (y_dtype == KIDI_F32) return by_tokens<false, float>(bn, map_w, map_x, p, token_tiles, stream);
+    if (y_dtype == KIDI_BF16) return by_tokens<false, bf16>(bn, map_w, map_x, map_y, p, blocks, stream);
+    if (y_dtype == KIDI_F32) return by_tokens<false, float>(bn, map_w, map_x, map_y, p, blocks, stream);
     return KIDI_REFUSED_DTYPE;
 }

@@ -2,10 +2,12 @@
 
 `gemm` / `gemm_silu_gate` compute y = x @ weight.T (or its fused SiLU gate) with the
 weight as the instruction's M operand, so that any number of rows of x, from one decoded
-token to a whole prompt, runs through the same kernel. With few rows the product is
-bound by reading the weight once; the kernel then splits K over several blocks, which
-needs a workspace and counters that this module keeps per device (allocated once, never
-replaced, so that captured graphs can hold their addresses).
+token to a whole prompt, runs through the same kernel: persistent blocks, the accumulator
+double-buffered in tensor memory, results written by TMA stores. With few rows the
+product is bound by reading the weight once; the kernel then deals the k-blocks of the
+tiles out over all blocks, which needs a workspace and counters that this module keeps
+per device (allocated once, never replaced, so that captured graphs can hold their
+addresses).
 
 KIDI_B200_TCGEN05_MAX_ROWS bounds the rows for which `fits` says yes (0 switches the
 kernel off); above it the caller uses the matrix library, which streams weights faster
@@ -24,12 +26,14 @@ from . import ops
 from .ops import _check, _need_cuda, _ptr, _stream, c_int, c_longlong, c_void_p, dtype_code
 
 MAX_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_MAX_ROWS", "16"))
+# From this many rows on (prompts) every product runs here again: whole tiles of 128 features x 256
+# tokens, one persistent block per SM (0 switches that off: the matrix library).
+PROMPT_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_PROMPT_ROWS", "1024"))
 MIN_FEATURES = 16384                    # the dispatcher uses this kernel for weights at least this tall
 MIN_GATED_ROWS = 9                      # and its fused SiLU gate from this many rows on (below: the skinny kernel)
 # The most rows for the fused gate (and within MAX_ROWS): beyond, the product followed by the gate kernel is faster.
 MAX_GATED_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_MAX_GATED_ROWS", "32"))
-WORKSPACE_FLOATS = 8 * 1024 * 1024      # 32 MiB of partial tiles
-COUNTERS = 16384
+COUNTERS = 4096                         # one per block of a launch (two blocks an SM at most)
 
 _bound = False
 _state: Dict[int, tuple] = {}
@@ -45,15 +49,21 @@ def _library():
         lib.kidi_gemm_tcgen05.restype = c_int
         lib.kidi_gemm_tcgen05_token_tile.argtypes = [c_int]
         lib.kidi_gemm_tcgen05_token_tile.restype = c_int
+        lib.kidi_gemm_tcgen05_workspace.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        lib.kidi_gemm_tcgen05_workspace.restype = c_longlong
         _bound = True
     return lib
 
 
 def _device_state(device: torch.device):
+    """(workspace, counters, error word) of a device: allocated once and never replaced, so that
+    captured graphs can hold their addresses. The workspace holds two partial tiles of 128
+    features x 256 tokens for each of the blocks that are resident at once."""
     index = device.index if device.index is not None else torch.cuda.current_device()
     state = _state.get(index)
     if state is None:
-        state = (torch.empty(WORKSPACE_FLOATS, dtype=torch.float32, device=device),
+        floats = 2 * 2 * attention_kernels.sm_count(device) * 128 * 256
+        state = (torch.empty(floats, dtype=torch.float32, device=device),
                  torch.zeros(COUNTERS, dtype=torch.int32, device=device),
                  torch.zeros(1, dtype=torch.int32, device=device))
         _state[index] = state
@@ -79,28 +89,19 @@ def fits(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return x.dim() == 2 and x.shape[0] <= MAX_ROWS and supports(x, weight)
 
 
-def choose_splits(rows: int, features: int, K: int, gated: bool, device: torch.device) -> int:
-    """Blocks per tile: enough that about two blocks per SM stream weights, each with at
-    least two 64-wide k-blocks, within the workspace."""
-    lib = _library()
-    tile = lib.kidi_gemm_tcgen05_token_tile(rows)
-    span = 64 if gated else 128
-    tiles = -(-features // span) * -(-rows // tile)
-    k_blocks = -(-K // 64)
-    wanted = (2 * attention_kernels.sm_count(device)) // max(1, tiles)
-    splits = max(1, min(wanted, k_blocks // 2, 32))
-    while splits > 1 and (tiles * splits * 128 * tile > WORKSPACE_FLOATS or tiles > COUNTERS):
-        splits -= 1
-    return splits
+def fits_prompt(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Many rows (a prompt): the compute-bound form of the kernel."""
+    return x.dim() == 2 and 0 < PROMPT_ROWS <= x.shape[0] and supports(x, weight)
 
 
 def _run(x, weight, out, features: int, gated: bool, splits: Optional[int], bias=None) -> None:
     _need_cuda(x, weight, out, bias)
     ops.check_bias(bias, features)
     rows, K = x.shape
-    if splits is None:
-        splits = choose_splits(rows, features, K, gated, x.device)
+    splits = int(splits or 0)            # 0: as many blocks as the GPU holds at once
     workspace, counters, error = _device_state(x.device)
+    if _library().kidi_gemm_tcgen05_workspace(rows, features, K, 1 if gated else 0, splits) > workspace.numel():
+        raise runtime_error("gemm_tcgen05: the workspace of this device is too small for the launch")
     _check(_library().kidi_gemm_tcgen05(
         _ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), rows, features, K, x.stride(0), weight.stride(0),
         out.stride(0), 1 if gated else 0, splits, _ptr(workspace), _ptr(counters), _ptr(error), _ptr(bias),

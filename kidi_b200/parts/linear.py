@@ -15,8 +15,10 @@ kernel runs follows the element types:
   (`kernels/tcgen05.py`: TMA-fed, accumulating in tensor memory), which streams such
   weights as fast as the vendor library does up to there (and takes up to 64 rows when
   KIDI_B200_TCGEN05_MAX_ROWS says so);
-* bfloat16 by bfloat16 otherwise: the vendor matrix library through `torch.mm`, which
-  is where the reference's CUDA engine calls a library too
+* bfloat16 by bfloat16 with 1,024 rows or more (prompts): the tcgen05 kernel again, in its
+  compute-bound form (whole tiles of 128 features x 256 tokens, a persistent block per SM);
+* bfloat16 by bfloat16 otherwise (17 to 1,023 rows): the vendor matrix library through
+  `torch.mm`, which is where the reference's CUDA engine calls a library too
   (docs/cuda-performance-plan.md:47-52).
 """
 from __future__ import annotations
@@ -70,7 +72,7 @@ class Linear:
         from ..kernels import tcgen05
         if skinny.fits(x, weight):
             return skinny.gemm(x, weight, out_dtype, out=out, bias=bias)
-        if weight.shape[0] >= tcgen05.MIN_FEATURES and tcgen05.fits(x, weight):
+        if (weight.shape[0] >= tcgen05.MIN_FEATURES and tcgen05.fits(x, weight)) or tcgen05.fits_prompt(x, weight):
             return tcgen05.gemm(x, weight, out_dtype, out=out, bias=bias)
         if weight.shape[1] % 8 or x.stride(0) % 8:  # the library wants 16-byte rows; keep odd widths exact
             return ops.gemm_simt(x, weight, out_dtype, out=out, bias=bias)

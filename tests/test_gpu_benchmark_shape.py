@@ -190,3 +190,33 @@ def test_other_forms_of_decode_attention_whole_model(shape_model, monkeypatch, f
     assert any(f"attention_decode[{form}]" in name for name in names), sorted(set(names))
     for index in range(count):
         assert relative_error(found[index], expected[index]) <= BF16_TOLERANCE, (form, index)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_a_long_prompt_at_the_benchmark_sizes(shape_model, dtype):
+    """A prompt of 1,100 tokens: from 1,024 rows on every product of the bfloat16 engine runs on this
+    package's tcgen05 kernel in its compute-bound form (whole tiles, persistent blocks, TMA stores)
+    and attention on the tcgen05 prompt kernel; no vendor-library product is left in the step."""
+    from kidi_b200 import StepBatch
+    from kidi_b200.kernels import ops
+    tensors, _, _ = shape_model
+    generator = np.random.default_rng(29)
+    tokens = generator.integers(0, SHAPE["vocab_size"], size=1100).tolist()
+    host = {name: tensor.float().cpu() for name, tensor in tensors.items()}
+    expected = plain_tail_logits(host, tokens, 3)
+    del host
+    engine = engine_of(shape_model, dtype)
+    slot = engine.acquire()
+    try:
+        with ops.record_launches() as names:
+            first = engine.step(StepBatch([slot], [tokens[:-1]], [[len(tokens) - 3, len(tokens) - 2]])).cpu().numpy()
+        last = engine.step(StepBatch([slot], [tokens[-1:]], None)).cpu().numpy()
+    finally:
+        engine.release(slot)
+    found = np.concatenate([first, last])
+    tolerance = BF16_TOLERANCE if dtype == "bfloat16" else FP32_TOLERANCE
+    assert relative_error(found, expected) <= tolerance, relative_error(found, expected)
+    if dtype == "bfloat16":
+        assert names.count("gemm_tcgen05") == 4 * SHAPE["num_hidden_layers"] and "library_mm" not in names, sorted(set(names))
+        assert "attention_prefill_tcgen05" in names
+    engine.check_device_errors()
