@@ -5,7 +5,12 @@ invalid rows rejected: ARCHITECTURE.md:612-616, src/kidi/inference/decoder.cpp:7
 its temperature and seed options exist for speech synthesis only, src/kidi/cli/main.cpp:898-899).
 Temperature sampling is this library's own: p = softmax(logits / T) in 32-bit and the
 inverse of the cumulative distribution at a uniform number keyed by (seed, sequence
-key, step), so that a sequence draws the same tokens whatever else is in its batch.
+key, step), so that a sequence's draw does not depend on what else is in its batch. In the
+32-bit engine the logits do not either (every kernel adds in an order that depends on the
+position only), so a sequence generates the same tokens in any batch; the bfloat16 engine
+chooses its product and attention kernels by the number of rows of a step, each of which
+rounds in its own order, so there the same holds up to that rounding (a token may differ
+where two logits lie closer together than it).
 Both run on the device (`kernels/ops.py`: argmax, sample).
 """
 from __future__ import annotations
