@@ -34,9 +34,14 @@ class RotaryEncoding(Part):
         # Built at first use, on the host in 32-bit, then moved to the device once.
         if self._tables is None:
             half = self.rotary_dim // 2
+            # The reference takes the power with the C library's 32-bit powf, which rounds correctly
+            # in all but rare cases; a vectorised 32-bit power may be one unit off in the last
+            # place, which the position multiplies (1e-4 in the cosine at position 1,000). So the
+            # power is taken in 64-bit from the 32-bit base and exponent and rounded once.
             index = torch.arange(half, dtype=torch.float32)
-            frequency = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float32),
-                                        (2.0 * index) / float(self.rotary_dim))
+            exponent = (2.0 * index) / torch.tensor(float(self.rotary_dim), dtype=torch.float32)
+            power = torch.pow(torch.tensor(self.theta, dtype=torch.float32).double(), exponent.double()).float()
+            frequency = 1.0 / power
             angle = torch.arange(self.max_positions, dtype=torch.float32)[:, None] * frequency[None, :]
             self._tables = (torch.cos(angle).contiguous().to(self.env.device),
                             torch.sin(angle).contiguous().to(self.env.device))

@@ -52,7 +52,9 @@ def rotary_tables(length: int, head_dim: int, theta: float):
     half = head_dim // 2
     frequency = np.empty(half, dtype=np.float32)
     for i in range(half):
-        frequency[i] = np.float32(1.0) / np.power(np.float32(theta), np.float32(2 * i) / np.float32(head_dim))
+        # powf of the C library: the correctly rounded 32-bit power of the 32-bit base and exponent.
+        power = np.float32(np.power(np.float64(np.float32(theta)), np.float64(np.float32(2 * i) / np.float32(head_dim))))
+        frequency[i] = np.float32(1.0) / power
     angle = np.arange(length, dtype=np.float32)[:, None] * frequency[None, :]
     return torch.from_numpy(np.cos(angle).astype(np.float32)), torch.from_numpy(np.sin(angle).astype(np.float32))
 
