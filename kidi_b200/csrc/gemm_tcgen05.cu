@@ -13,18 +13,21 @@
 // double-buffered in tensor memory, so that the epilogue of one tile runs under the
 // products of the next and the ring of operand stages never drains between tiles.
 //
-// The k-blocks of all tiles are dealt out evenly over the blocks (see the kernel): with few
-// tokens, where the product is bound by reading W once, that is split-K and every SM streams
-// weights; with many it fills the last round of blocks. Parts of tiles meet in a workspace and
-// the last block to arrive for a tile (an atomic counter) adds them in their order along k,
-// so the result does not depend on timing. Epilogues: store
-// (bfloat16 or float32), or the SiLU gate of a fused [gate | up] projection, for which a
-// tile is 64 gate rows and the 64 matching up rows.
+// With fewer tiles than resident blocks (few tokens: the product is bound by reading W once) the
+// tiles' k-blocks are dealt out evenly over the blocks, so that every SM streams weights (split-K).
+// A block writes its part of a tile to a workspace and counts itself in; when all parts of the tile
+// are there (the blocks are launched cooperatively, so they are resident together), the block that
+// brought the i-th part adds the i-th share of the tile's token columns over all parts, in their
+// order along k, so that the result does not depend on timing, and stores it: the sum and the
+// stores are spread over the blocks. Epilogues: store (bfloat16 or float32), or the SiLU gate of a
+// fused [gate | up] projection, for which a tile is 64 gate rows and the 64 matching up rows.
 //
 // Every wait on an mbarrier is bounded: when the limit is reached the block records a
 // code in `error`, waits (bounded) for its copies in flight, frees its tensor memory
 // and returns.
 #include <cuda.h>
+
+#include <atomic>
 #include <string.h>
 
 #include "common.cuh"
@@ -134,7 +137,7 @@ __device__ __forceinline__ void tmem_load_16(unsigned address, float (&v)[16]) {
 struct Params {
     void* y;               // [tokens, ldy]
     float* workspace;      // [2 * blocks][BM][BN] partial tiles
-    int* counters;         // [blocks], zero between calls (the kernel leaves them zero)
+    int* counters;         // [2 * blocks]: parts arrived, parts read; zero between calls (the kernel leaves them zero)
     int* error;            // set to a non-zero code when a bounded wait ran out
     const float* bias;     // [features] added to every token's row, or null (not with the gate)
     long long ldy;
@@ -305,6 +308,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int quarter = warp & 3;                     // TMEM lanes 32 * quarter .. + 31
         const int row = quarter * 32 + lane;              // row of the tile = TMEM lane
         int done = 0, staged_chunks = 0;
+        // The shared tiles this block has brought a part of (the second phase below).
+        long long shared_tile[2];
+        int shared_first[2], shared_count[2], shared_parts = 0;
         // `tail_tile` < 0: a whole tile of this block's own; else the tile's number within the tail, of
         // which this block brings k-blocks kb_first .. kb_first + kb_count - 1.
         auto finish = [&](long long tile, long long tail_tile, int kb_first, int kb_count) {
@@ -321,11 +327,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             // A shared tile: the blocks that hold its first and last k-block, the parts between them.
             const int first_block = whole ? 0 : block_of(tail_tile * p.k_blocks);
             const int parts = whole ? 1 : block_of((tail_tile + 1) * p.k_blocks - 1) - first_block + 1;
-            bool reduce = false;
             if (!whole) {
                 // This part to the workspace (a block has at most two parts: the one its piece begins
-                // with and the one it ends with), column by column so that a warp writes whole lines;
-                // the block that brings the last part adds all of them.
+                // with and the one it ends with), column by column so that a warp writes whole lines.
                 const long long slot = 2LL * blockIdx.x + (kb_first > 0 || piece_begin == tail_tile * p.k_blocks ? 0 : 1);
                 float* mine = p.workspace + slot * BM * BN + row;
 #pragma unroll 1
@@ -336,38 +340,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                         for (int i = 0; i < 16; ++i) v[i] = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) mine[(long long)(c + i) * BM] = v[i];
+                    for (int i = 0; i < 16; ++i) __stcg(mine + (long long)(c + i) * BM, v[i]);
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbarrier_arrive(&drained_bar[buffer]);       // the tensor core may have the accumulator back
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (threadIdx.x == 64) is_last = atomicAdd(p.counters + first_block, 1) == parts - 1;
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                reduce = is_last != 0;
-                if (reduce) __threadfence();
+                if (threadIdx.x == 64) atomicAdd(p.counters + first_block, 1);   // this part has arrived
+                if (shared_parts < 2) {
+                    shared_tile[shared_parts] = tile;
+                    shared_first[shared_parts] = first_block;
+                    shared_count[shared_parts] = parts;
+                    ++shared_parts;
+                }
+                return;
             }
-            if (whole || reduce) {
+            {
                 TY* y = (TY*)p.y;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     float v[16];
-                    if (whole) {
-                        if (ok) tmem_load_16(accumulator + c, v);
-                        else
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                    } else {
+                    if (ok) tmem_load_16(accumulator + c, v);
+                    else
 #pragma unroll
                         for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                        for (int part = 0; part < parts; ++part) {  // in their order along k: the sum does not depend on timing
-                            const long long holder = first_block + part;
-                            const long long slot = 2 * holder + (begin_of(holder) >= tail_tile * p.k_blocks ? 0 : 1);
-                            const float* from = p.workspace + slot * BM * BN + (long long)c * BM + row;
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) v[i] += __ldcg(from + i * BM);
-                        }
-                    }
                     bool mine = f0 + row < p.features;    // this thread has results of this chunk
                     if (GATED) {
                         // Rows 64..127 hold the up projection of the features in rows 0..63.
@@ -405,11 +401,85 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         }
                     }
                 }
-                if (whole) {
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    mbarrier_arrive(&drained_bar[buffer]);
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbarrier_arrive(&drained_bar[buffer]);
+            }
+        };
+        // A shared tile's second phase: when all its parts have arrived (the blocks of a call are
+        // resident together: a cooperative launch), the block that brought the i-th part adds, in the
+        // parts' order along k, the i-th share of the tile's token columns, and stores them.
+        auto combine = [&](long long tile, int first_block, int parts) {
+            int token_tile, feature_tile;
+            locate(tile, token_tile, feature_tile);
+            const int f0 = feature_tile * SPAN, t0 = token_tile * BN;
+            const long long tail_tile = tile - p.tail_first;
+            if (threadIdx.x == 64) {
+                unsigned spin = 0;
+                while (*abort_flag == 0) {
+                    int arrived;
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(arrived) : "l"(p.counters + first_block) : "memory");
+                    if (arrived >= parts) break;
+                    if (++spin >= (SPIN_LIMIT >> 4)) { *abort_flag = 1; atomicExch(p.error, 5); }   // about a second
                 }
-                if (reduce && threadIdx.x == 64) p.counters[first_block] = 0;  // ready for the next call
+                is_last = *abort_flag;                     // one reading of the flag for all (the barriers below)
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const bool aborted = is_last != 0;
+            __threadfence();
+            TY* y = (TY*)p.y;
+            const int share = (BN + parts - 1) / parts;
+            const int first = (blockIdx.x - first_block) * share;
+            const int count = aborted ? 0 : max(0, min(share, min(BN, p.tokens - t0) - first));
+            const float shift = (!GATED && p.bias && f0 + row < p.features) ? p.bias[f0 + row] : 0.f;
+#pragma unroll 1
+            for (int j0 = 0; j0 < count; j0 += 16) {
+                // Sixteen columns at a time and four parts' values asked for at once (64 loads in flight a
+                // thread: the parts come from other SMs through the L2), added in the parts' order along k.
+                float sum[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) sum[j] = 0.f;
+#pragma unroll 1
+                for (int part0 = 0; part0 < parts; part0 += 4) {
+                    float v[4][16];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const long long holder = first_block + min(part0 + q, parts - 1);
+                        const long long slot = 2 * holder + (begin_of(holder) >= tail_tile * p.k_blocks ? 0 : 1);
+                        const float* from = p.workspace + slot * BM * BN + (long long)(first + j0) * BM + row;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            v[q][j] = (part0 + q < parts && j0 + j < count) ? __ldcg(from + j * BM) : 0.f;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) sum[j] += v[q][j];
+                }
+                if (GATED) {
+                    // Rows 64..127 hold the up projection of the features in rows 0..63.
+                    if (row >= 64)
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) exchange[(row - 64) * 17 + j] = sum[j];
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (row < 64 && f0 + row < p.features)
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j0 + j < count)
+                                y[(long long)(t0 + first + j0 + j) * p.ldy + f0 + row] =
+                                    from_float<TY>(sum[j] / (1.0f + expf(-sum[j])) * exchange[row * 17 + j]);
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                } else if (f0 + row < p.features) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (j0 + j < count)
+                            y[(long long)(t0 + first + j0 + j) * p.ldy + f0 + row] = from_float<TY>(sum[j] + shift);
+                }
+            }
+            // The last block to have read the parts leaves the tile's counters at zero for the next call.
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64 && atomicAdd(p.counters + gridDim.x + first_block, 1) == parts - 1) {
+                p.counters[first_block] = 0;
+                p.counters[gridDim.x + first_block] = 0;
             }
         };
         for (int round = 0; round < p.rounds; ++round)
@@ -422,6 +492,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             finish(p.tail_first + tail_tile, tail_tile, kb_first, kb_count);
             g += kb_count;
         }
+        for (int i = 0; i < shared_parts; ++i) combine(shared_tile[i], shared_first[i], shared_count[i]);
         if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the last stores have left
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -488,23 +559,64 @@ int make_store_map(CUtensorMap* map, void* base, long long tokens, long long fea
     return status == CUDA_SUCCESS ? 0 : 1000 + (int)status;
 }
 
+// Shared memory of a block: the stages, a kilobyte to align them, the gated epilogue's exchange
+// buffer and two buffers of results on their way out.
+template <int BN, int STAGES>
+constexpr size_t shared_bytes() {
+    return (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 64 * 17 * sizeof(float) + 2 * 16 * BM * sizeof(bf16);
+}
+
+// Sets the kernel up (once) and returns how many of its blocks the device promises to hold on an SM
+// at a time, which bounds a cooperative launch (0: the set-up failed). For a kernel that allocates
+// tensor memory the device reports one, whatever its other needs; two such blocks do run on an SM
+// together where shared memory and tensor memory allow (measured), which launches whose blocks do not
+// wait for each other make use of.
+template <int BN, int STAGES, bool GATED, typename TY>
+int blocks_per_sm() {
+    constexpr size_t shared = shared_bytes<BN, STAGES>();
+    static_assert(shared <= (BN <= 64 ? 113 : 227) * 1024, "the stages fit an SM's shared memory (twice for small tiles)");
+    static std::atomic<int> known{-1};
+    int value = known.load(std::memory_order_acquire);
+    if (value < 0) {
+        auto kernel = gemm_tcgen05_kernel<BN, STAGES, GATED, TY>;
+        value = 0;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) == cudaSuccess &&
+            cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) ==
+                cudaSuccess) {
+            int found = 0;
+            cudaError_t status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&found, kernel, THREADS, shared);
+            if (status == cudaSuccess)
+                value = found > 2 ? 2 : found;             // tensor memory: two accumulator pairs an SM at most anyway
+        }
+        known.store(value, std::memory_order_release);
+    }
+    return value;
+}
+
 template <int BN, int STAGES, bool GATED, typename TY>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const CUtensorMap& map_y, const Params& p, int blocks,
            cudaStream_t stream) {
-    // The stages, a kilobyte to align them, the gated epilogue's exchange buffer and two buffers of
-    // results on their way out.
-    constexpr size_t shared = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 64 * 17 * sizeof(float) +
-                              2 * 16 * BM * sizeof(bf16);
-    static_assert(shared <= (BN <= 64 ? 113 : 227) * 1024, "the stages fit an SM's shared memory (twice for small tiles)");
+    constexpr size_t shared = shared_bytes<BN, STAGES>();
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, GATED, TY>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        if (status != cudaSuccess) return (int)status;
-        configured = true;
+    const int per_sm = blocks_per_sm<BN, STAGES, GATED, TY>();
+    if (per_sm <= 0) return KIDI_REFUSED_SIZE;
+    if (p.rounds > 0) {
+        kernel<<<blocks, THREADS, shared, stream>>>(map_w, map_x, map_y, p);
+        return kidi_launch_status();
     }
-    kernel<<<blocks, THREADS, shared, stream>>>(map_w, map_x, map_y, p);
-    return kidi_launch_status();
+    // Shared tiles: blocks wait for each other's parts, so they must be resident together.
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(blocks, 1, 1);
+    config.blockDim = dim3(THREADS, 1, 1);
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeCooperative;
+    attribute[0].val.cooperative = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    cudaError_t status = cudaLaunchKernelEx(&config, kernel, map_w, map_x, map_y, p);
+    return status != cudaSuccess ? (int)status : kidi_launch_status();
 }
 
 template <bool GATED, typename TY>
@@ -526,19 +638,58 @@ KIDI_API int kidi_gemm_tcgen05_token_tile(int tokens) {
     return tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : tokens <= 128 ? 128 : 256;
 }
 
-// How many blocks a call launches: as many as are resident at once (two per SM up to 64 tokens, one
-// above), or, when there are fewer tiles than that, a multiple of the tiles (so that no block's
-// piece lies in two tiles): `splits` > 0 asks for that many blocks per tile, 0 for as many as fit.
+namespace {
+template <bool GATED>
+int blocks_per_sm_of(int bn) {
+    switch (bn) {
+        case 16: return blocks_per_sm<16, 5, GATED, bf16>();
+        case 32: return blocks_per_sm<32, 4, GATED, bf16>();
+        case 64: return blocks_per_sm<64, 4, GATED, bf16>();
+        case 128: return blocks_per_sm<128, 6, GATED, bf16>();
+        case 256: return blocks_per_sm<256, 4, GATED, bf16>();
+    }
+    return 0;
+}
+}  // namespace
+
+// Blocks of the kernel for `tokens` rows that are surely resident on an SM together (as the device
+// reports it: the bound of a cooperative launch).
+KIDI_API int kidi_gemm_tcgen05_blocks_per_sm(int tokens, int gated) {
+    const int bn = kidi_gemm_tcgen05_token_tile(tokens);
+    return gated ? blocks_per_sm_of<true>(bn) : blocks_per_sm_of<false>(bn);
+}
+
+// How many blocks a call launches. With at least as many tiles as blocks that are surely resident
+// together, blocks take whole tiles: one each, up to what the SMs hold at a time (two per SM up to 64
+// tokens, one above), and rounds of tiles beyond that. With fewer tiles the tiles are shared: as many
+// blocks as are surely resident together and get at least four k-blocks each (`splits` > 0 asks
+// for that many blocks per tile instead).
 KIDI_API int kidi_gemm_tcgen05_blocks(int tokens, int features, int K, int gated, int splits) {
     const int bn = kidi_gemm_tcgen05_token_tile(tokens);
     const long long tiles = (long long)((features + (gated ? 64 : BM) - 1) / (gated ? 64 : BM)) * ((tokens + bn - 1) / bn);
     const int k_blocks = (K + BK - 1) / BK;
-    const long long resident = (long long)sm_count_of_current_device() * (bn <= 64 ? 2 : 1);
-    if (tiles >= resident) return (int)resident;
-    long long per_tile = resident / tiles;
-    if (splits > 0 && splits < per_tile) per_tile = splits;
-    if (per_tile > k_blocks) per_tile = k_blocks;
-    return (int)(tiles * (per_tile < 1 ? 1 : per_tile));
+    const int per_sm = kidi_gemm_tcgen05_blocks_per_sm(tokens, gated);
+    const long long sms = sm_count_of_current_device();
+    const long long together = sms * (per_sm > 0 ? per_sm : 1), at_a_time = sms * (bn <= 64 ? 2 : 1);
+    if (tiles >= together) return (int)(tiles < at_a_time ? tiles : at_a_time);
+    if (splits > 0) {
+        long long per_tile = together / tiles;
+        if (splits < per_tile) per_tile = splits;
+        if (per_tile > k_blocks) per_tile = k_blocks;
+        return (int)(tiles * (per_tile < 1 ? 1 : per_tile));
+    }
+    if (bn >= 128) {
+        // Wide tiles: a part's trip through the workspace is long, so a tile is shared only by whole
+        // multiples of blocks (measured at 512 rows: 53 us with the k-blocks dealt out evenly over all
+        // SMs against 32 us with a block per tile on two thirds of them).
+        long long per_tile = together / tiles;
+        if (per_tile > k_blocks / 4) per_tile = k_blocks / 4;
+        return (int)(tiles * (per_tile < 1 ? 1 : per_tile));
+    }
+    // The tiles' k-blocks dealt out evenly, a block's piece being at least four of them.
+    long long blocks = tiles * k_blocks / 4;
+    if (blocks > together) blocks = together;
+    return (int)(blocks < tiles ? tiles : blocks);
 }
 
 // Floats of workspace a call needs (two partial tiles a block) and, in counters, its number of blocks.
@@ -549,7 +700,7 @@ KIDI_API long long kidi_gemm_tcgen05_workspace(int tokens, int features, int K, 
 
 // x [tokens, K] and w [features (2 * features when gated), K] bfloat16, rows 16-byte
 // aligned; y [tokens, features] bfloat16 or float32. `workspace` (kidi_gemm_tcgen05_workspace
-// floats), `counters` (one per block; zeroed once by the caller; the kernel leaves them zero) and
+// floats), `counters` (two per block; zeroed once by the caller; the kernel leaves them zero) and
 // `error` are the caller's. `bias` (float32 [features], or null) is added to every row.
 KIDI_API int kidi_gemm_tcgen05(const void* x, const void* w, void* y, int y_dtype, int tokens, int features, int K,
                                long long ldx, long long ldw, long long ldy, int gated, int splits, float* workspace,

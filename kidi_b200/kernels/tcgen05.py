@@ -33,7 +33,7 @@ MIN_FEATURES = 16384                    # the dispatcher uses this kernel for we
 MIN_GATED_ROWS = 9                      # and its fused SiLU gate from this many rows on (below: the skinny kernel)
 # The most rows for the fused gate (and within MAX_ROWS): beyond, the product followed by the gate kernel is faster.
 MAX_GATED_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_MAX_GATED_ROWS", "32"))
-COUNTERS = 4096                         # one per block of a launch (two blocks an SM at most)
+COUNTERS = 4096                         # two per block of a launch (two blocks an SM at most)
 
 _bound = False
 _state: Dict[int, tuple] = {}
