@@ -1,7 +1,8 @@
 """Parts of other kinds than the package has, defined here and registered from outside:
 a feed-forward that routes every token to two of four small experts, a position table
-that is added to the embeddings, and a rotary encoding of half the head with slowed
-positions. Each is built from a specification, given random weights through the
+that is added to the embeddings, a rotary encoding of half the head with slowed
+positions, a norm that subtracts the mean and has a bias, and a block that runs mixer and
+feed-forward side by side. Each is built from a specification, given random weights through the
 package's own writer, loaded by tensor name and stepped through the engine (whole
 requests, chunks, batches of unequal lengths, single tokens) against a plain model
 written here. They are toys: no model of anyone's.
@@ -273,3 +274,106 @@ def test_toy_position_encodings(tmp_path, dtype):
     engine = Engine.load(folder, dtype=dtype, max_tokens=2048)
     run_every_way(engine, requests, expected, FP32_TOLERANCE if dtype == "float32" else BF16_TOLERANCE,
                   f"toy positions {dtype}")
+
+
+# ------------------------------------------------- another norm and another arrangement
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_norm_in_a_toy_arrangement(tmp_path, dtype):
+    """A norm that subtracts the mean and has a bias, and a block that runs mixer and feed-forward
+    side by side from one norm (out = x + mixer(n(x)) + feed_forward(n(x))), in the second of two
+    layers; the first keeps the package's pre-norm block, whose last product must not prepare rows
+    for a norm that it does not know. The final norm is the toy's too."""
+    from kidi_b200 import Engine, register_architecture, register_part, write_random_model
+    from kidi_b200.models import qwen3
+    from kidi_b200.parts.base import Part, plain_rows
+    from kidi_b200.parts.spec import LayerSpec, ParamSpec, PartSpec
+
+    @register_part("norm", "toy_centred")
+    class ToyCentredNorm(Part):
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.size, self.eps = int(spec.param("size")), float(spec.param("eps"))
+
+        def parameter_specs(self):
+            return [ParamSpec("weight", (self.size,), init=("one_plus_normal", 0.1)),
+                    ParamSpec("bias", (self.size,), init=("normal", 0.1))]
+
+        def bind(self, tensors):
+            self.weight, self.bias = tensors["weight"].float(), tensors["bias"].float()
+
+        def forward(self, stream, rows=None, scaled=False):
+            delta = stream.take_pending()
+            hidden = stream.hidden
+            if rows is not None:                      # only these rows, the stream stays as it is
+                hidden = hidden[rows.long()]
+                if delta is not None:
+                    hidden = hidden + delta[rows.long()].float()
+            elif delta is not None:
+                hidden += delta.float()
+            centred = hidden - hidden.mean(dim=-1, keepdim=True)
+            normed = centred * torch.rsqrt(centred.square().mean(dim=-1, keepdim=True) + self.eps)
+            return (normed * self.weight + self.bias).to(self.env.dtype)
+
+    @register_part("arrangement", "toy_side_by_side")
+    class ToySideBySide(Part):
+        ROLES = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+        def __init__(self, spec, env, parts):
+            super().__init__(spec, env)
+            self.norm, self.mixer, self.feed_forward = parts["norm"], parts["mixer"], parts["feed_forward"]
+
+        def children(self):
+            return (self.norm, self.mixer, self.feed_forward)
+
+        def cache_requests(self):
+            return self.mixer.cache_requests()
+
+        def first_norm(self):
+            return self.norm
+
+        def forward(self, stream, ctx, views, owns_cache):
+            normed = plain_rows(self.norm.forward(stream))
+            mixed = self.mixer.forward(normed, ctx, views, owns_cache)
+            stream.add(mixed.float() + self.feed_forward.forward(normed, ctx).float())
+
+    Config = wrapped_config(())
+
+    def build(config):
+        spec = qwen3.build_spec(config.base)
+        centred = {"size": config.base.hidden_size, "eps": config.base.rms_norm_eps}
+        second = spec.layers[1]
+        side_by_side = LayerSpec(PartSpec("toy_side_by_side"), {
+            "norm": PartSpec("toy_centred", centred, "model.layers.1.input_layernorm."),
+            "mixer": second.parts["mixer"], "feed_forward": second.parts["feed_forward"]})
+        return dataclasses.replace(spec, architecture="ToyNormForCausalLM", layers=(spec.layers[0], side_by_side),
+                                   final_norm=PartSpec("toy_centred", centred, "model.norm."))
+
+    register_architecture("ToyNormForCausalLM", Config, build)
+    raw = dict(BASE, architectures=["ToyNormForCausalLM"])
+    folder = write_random_model(raw, str(tmp_path / "norms"), seed=31, dtype=torch.bfloat16)
+    sharpen_logits(folder)
+    config, tensors = plain_model.read_model_folder(folder)
+    assert "model.layers.1.post_attention_layernorm.weight" not in tensors and "model.norm.bias" in tensors
+    eps = config["rms_norm_eps"]
+    cos, sin = plain_model.rotary_tables(320, config["head_dim"], plain_model.rope_theta(config))
+
+    def centred_norm(x, prefix):
+        weight, bias = tensors[prefix + "weight"].double(), tensors[prefix + "bias"].double()
+        centred = x - x.mean(dim=-1, keepdim=True)
+        return centred * torch.rsqrt(centred.square().mean(dim=-1, keepdim=True) + eps) * weight + bias
+
+    def whole(tokens):
+        hidden = plain_model.embed(tokens, tensors["model.embed_tokens.weight"], torch.float64)
+        n = len(tokens)
+        hidden = plain_model.block(hidden, tensors, 0, config, cos[:n].double(), sin[:n].double(), None)
+        normed = centred_norm(hidden, "model.layers.1.input_layernorm.")
+        hidden = hidden + plain_model.attention_layer(normed, tensors, "model.layers.1.self_attn.", config,
+                                                cos[:n].double(), sin[:n].double(), None) \
+            + plain_model.gated_feed_forward(normed, tensors, "model.layers.1.mlp.")
+        return (centred_norm(hidden, "model.norm.") @ tensors["lm_head.weight"].double().T).float().numpy()
+
+    requests = rh.random_requests(config["vocab_size"], [2, 64, 129, 257, 320], seed=32)
+    expected = {name: whole(tokens) for name, tokens in requests.items()}
+    engine = Engine.load(folder, dtype=dtype, max_tokens=2048)
+    run_every_way(engine, requests, expected, FP32_TOLERANCE if dtype == "float32" else BF16_TOLERANCE,
+                  f"toy norm and arrangement {dtype}")
