@@ -11,7 +11,7 @@ addresses).
 
 KIDI_B200_TCGEN05_MAX_ROWS bounds the rows for which `fits` says yes (0 switches the
 kernel off); above it the caller uses the matrix library, which streams weights faster
-from 17 rows on.
+from 17 rows on, except weights as tall as an output head (KIDI_B200_TCGEN05_MAX_ROWS_TALL).
 """
 from __future__ import annotations
 
@@ -30,6 +30,11 @@ MAX_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_MAX_ROWS", "16"))
 # tokens, one persistent block per SM (0 switches that off: the matrix library).
 PROMPT_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_PROMPT_ROWS", "1024"))
 MIN_FEATURES = 16384                    # the dispatcher uses this kernel for weights at least this tall
+# A weight as tall as an output head (over a thousand tiles: rounds of whole tiles, no shared ones) streams
+# as fast as through the matrix library up to this many rows (151,936 x 4,096: 207 against 214 us at 24 and
+# 32 rows, 214 against 213 at 64, with 32-bit results against the library's 16-bit ones).
+TALL_FEATURES = 65536
+MAX_ROWS_TALL = int(os.environ.get("KIDI_B200_TCGEN05_MAX_ROWS_TALL", "64"))
 MIN_GATED_ROWS = 9                      # and its fused SiLU gate from this many rows on (below: the skinny kernel)
 # The most rows for the fused gate (and within MAX_ROWS): beyond, the product followed by the gate kernel is faster.
 MAX_GATED_ROWS = int(os.environ.get("KIDI_B200_TCGEN05_MAX_GATED_ROWS", "32"))
@@ -86,7 +91,9 @@ def supports(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def fits(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    return x.dim() == 2 and x.shape[0] <= MAX_ROWS and supports(x, weight)
+    if x.dim() != 2 or not supports(x, weight):
+        return False
+    return x.shape[0] <= MAX_ROWS or (x.shape[0] <= MAX_ROWS_TALL and weight.shape[0] >= TALL_FEATURES)
 
 
 def fits_prompt(x: torch.Tensor, weight: torch.Tensor) -> bool:

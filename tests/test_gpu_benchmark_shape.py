@@ -131,9 +131,9 @@ EXPECTED_KERNELS = {
     8: ["gemm_skinny[row factors]", "gemm_skinny[into the residual]", "gemm_silu_gate[skinny]", "attention_decode[cluster]"],
     12: ["library_mm", "gemm_silu_gate[tcgen05]", "gemm_tcgen05", "attention_decode[cluster]"],
     16: ["library_mm", "gemm_silu_gate[tcgen05]", "gemm_tcgen05", "attention_decode[cluster]"],
-    24: ["library_mm", "silu_gate", "attention_decode[cluster]"],
-    32: ["library_mm", "silu_gate", "attention_decode[one block]"],     # 24 sequences padded by the graph
-    64: ["library_mm", "silu_gate", "attention_decode[ring]"],
+    24: ["library_mm", "silu_gate", "gemm_tcgen05", "attention_decode[cluster]"],        # the head: tcgen05
+    32: ["library_mm", "silu_gate", "gemm_tcgen05", "attention_decode[one block]"],     # 24 sequences padded by the graph
+    64: ["library_mm", "silu_gate", "gemm_tcgen05", "attention_decode[ring]"],
 }
 
 

@@ -70,6 +70,7 @@ def test_which_product_a_shape_goes_to():
     assert not skinny.fits(*operands(9, 4096))
     assert not skinny.fits(*operands(8, 4096, width=4100))        # rows that 16-byte vectors cannot read
     assert tcgen05.fits(*operands(16, 24576)) and not tcgen05.fits(*operands(17, 24576))
+    assert tcgen05.fits(*operands(64, 65536)) and not tcgen05.fits(*operands(65, 65536))   # as tall as an output head
     assert tcgen05.fits_prompt(*operands(2048, 4096)) and tcgen05.fits_prompt(*operands(1024, 6144))
     assert not tcgen05.fits_prompt(*operands(1023, 4096)) and not tcgen05.fits_prompt(*operands(2048, 4096, width=4100))
     assert tcgen05.MIN_GATED_ROWS == skinny.MAX_ROWS + 1          # no batch size falls between the two kernels
