@@ -398,7 +398,9 @@ def main() -> int:
                 "h2d_bytes_per_step": round(e2e_stats.host_to_device_bytes / max(1, e2e_stats.decode_steps), 1),
                 "d2h_bytes_per_step": 4 * batch, "steps": e2e_stats.decode_steps,
                 "note": "a step's input tokens are its predecessor's output on the device; the host copies the "
-                        "batch's tables up when decoding starts and reads every step's tokens back"},
+                        "batch's tables up when decoding starts and reads every step's tokens back; decoding "
+                        "starts right after the prompts, whose power draw leaves lowered clocks for the first "
+                        "twenty steps or so (4.3, then 3.9 ms a step)"},
         "gpu_launches": main_run["kernels_per_step"] * steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4), "of": peak["source"]},
