@@ -575,8 +575,11 @@ template <int BN, int STAGES, bool GATED, typename TY>
 int blocks_per_sm() {
     constexpr size_t shared = shared_bytes<BN, STAGES>();
     static_assert(shared <= (BN <= 64 ? 113 : 227) * 1024, "the stages fit an SM's shared memory (twice for small tiles)");
-    static std::atomic<int> known{-1};
-    int value = known.load(std::memory_order_acquire);
+    static std::atomic<int> known_by_device[64];         // 0: not asked yet; else the answer + 1
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+    std::atomic<int>& known = known_by_device[device];
+    int value = known.load(std::memory_order_acquire) - 1;
     if (value < 0) {
         auto kernel = gemm_tcgen05_kernel<BN, STAGES, GATED, TY>;
         value = 0;
@@ -588,7 +591,7 @@ int blocks_per_sm() {
             if (status == cudaSuccess)
                 value = found > 2 ? 2 : found;             // tensor memory: two accumulator pairs an SM at most anyway
         }
-        known.store(value, std::memory_order_release);
+        known.store(value + 1, std::memory_order_release);
     }
     return value;
 }
