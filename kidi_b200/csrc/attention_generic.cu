@@ -274,6 +274,8 @@ struct AttentionArgs {
     const int* seq_row0;  // first packed row of the sequence
     int rows, heads, kv_heads, head_dim, window;  // window 0: every earlier key is visible
     float scale;
+    float softcap;        // > 0: a score s becomes softcap * tanh(s / softcap)
+    const float* slopes;  // [heads] or null: head h adds slopes[h] * (key position - query position) to a score
 };
 
 // One block of 4 warps per (row, head). Warp w takes keys lo+w, lo+w+4, ... in
@@ -325,7 +327,9 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(AttentionArgs a)
             const int c = lane + 32 * i;
             if (c < d) dot = fmaf(query[c], to_float(key[c]), dot);
         }
-        const float score = warp_sum(dot) * a.scale;
+        float score = warp_sum(dot) * a.scale;
+        if (a.softcap > 0.f) score = a.softcap * tanhf(score / a.softcap);
+        if (a.slopes) score += a.slopes[head] * (float)(u - position);
         const float next = fmaxf(best, score);
         const float keep = expf(best - next);  // 0 on the first key (best = -inf)
         const float weight = expf(score - next);

@@ -228,7 +228,8 @@ def fuses_rotation(plan, qkv: torch.Tensor, *, heads: int, kv_heads: int, head_d
 
 
 def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step, rotation=None,
-        step_rows_cached: bool = False, splits: Optional[int] = None, ring: Optional[bool] = None) -> None:
+        step_rows_cached: bool = False, splits: Optional[int] = None, ring: Optional[bool] = None,
+        softcap: float = 0.0, slopes: Optional[torch.Tensor] = None) -> None:
     """`ctx` gives the step's `plan`, its device `tables` and `workspace(name, count, zero)`.
     `keys_in_step`: the step's own keys and values are read from qkv (else from the
     cache, like the earlier ones). `step_rows_cached`: they are in the cache as well (a cache
@@ -239,9 +240,14 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
     override the launcher's own choice of the decode kernel's form (tests of each form)."""
     plan, tables = ctx.plan, ctx.tables
     decode = plan.is_decode and not keys_in_step
-    if not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode) or (kv_view is not None and kv_view.page_size != 64):
+    # Scores that are bounded or shifted by position run on the general kernel (the tensor-core kernels
+    # compute plain scaled scores).
+    reshaped = bool(softcap) or slopes is not None
+    if (reshaped or not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode)
+            or (kv_view is not None and kv_view.page_size != 64)):
         ops.attention_generic(qkv, out, heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale,
-                              window=window, tables=tables, kv_view=kv_view, keys_in_step=keys_in_step)
+                              window=window, tables=tables, kv_view=kv_view, keys_in_step=keys_in_step,
+                              softcap=softcap, slopes=slopes)
         return
     if not decode and tensor_memory_fits(qkv, out, head_dim, heads, kv_heads, scale):
         common = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
@@ -327,21 +333,27 @@ class AttentionLauncher:
     and the launch. Each part (hence each group of layers with a geometry of its own) chooses the
     form of its decode kernel itself, from the rows of the step and the longest sequence."""
 
-    def __init__(self, *, heads: int, kv_heads: int, head_dim: int, scale: float, window=None):
+    def __init__(self, *, heads: int, kv_heads: int, head_dim: int, scale: float, window=None,
+                 softcap: float = 0.0, slopes: Optional[torch.Tensor] = None):
         self.geometry = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim)
         self.scale, self.window = scale, window
+        # Scores bounded by softcap * tanh(s / softcap), or shifted by slopes[head] * (key - query position):
+        # such scores run on the general kernel.
+        self.softcap, self.slopes = float(softcap or 0.0), slopes
+        self.reshaped = bool(self.softcap) or slopes is not None
 
     def fuses_rotation(self, plan, qkv, **arguments) -> bool:
         """Whether `run` can do norm, rotation and the cache write of this step itself."""
-        return fuses_rotation(plan, qkv, **self.geometry, **arguments)
+        return not self.reshaped and fuses_rotation(plan, qkv, **self.geometry, **arguments)
 
     def run(self, ctx, qkv, out, **arguments) -> None:
-        run(ctx, qkv, out, scale=self.scale, window=self.window, **self.geometry, **arguments)
+        run(ctx, qkv, out, scale=self.scale, window=self.window, softcap=self.softcap, slopes=self.slopes,
+            **self.geometry, **arguments)
 
     def launch_signature(self, dtype: torch.dtype, rows: int, longest: int, device: torch.device) -> tuple:
         """What a captured decode step freezes of this launcher's choices: the form of the
         tensor-core decode kernel (the general kernel, which the 32-bit engine runs, has none)."""
         geometry = self.geometry
-        if not fast_fits(dtype, geometry["heads"], geometry["kv_heads"], geometry["head_dim"], True):
+        if self.reshaped or not fast_fits(dtype, geometry["heads"], geometry["kv_heads"], geometry["head_dim"], True):
             return ()
         return decode_form(rows, geometry["kv_heads"], geometry["head_dim"], longest, self.window, device)

@@ -140,7 +140,8 @@ class AttentionArgs(ctypes.Structure):
                 ("ldkv", c_longlong), ("k_cache", c_void_p), ("v_cache", c_void_p), ("cache", CacheGeometry),
                 ("out", c_void_p), ("ldo", c_longlong), ("row_seq", c_void_p), ("row_pos", c_void_p),
                 ("seq_slot", c_void_p), ("seq_start", c_void_p), ("seq_row0", c_void_p), ("rows", c_int),
-                ("heads", c_int), ("kv_heads", c_int), ("head_dim", c_int), ("window", c_int), ("scale", c_float)]
+                ("heads", c_int), ("kv_heads", c_int), ("head_dim", c_int), ("window", c_int), ("scale", c_float),
+                ("softcap", c_float), ("slopes", c_void_p)]
 
 
 def cache_geometry(view, kv_heads: int, head_dim: int) -> CacheGeometry:
@@ -293,10 +294,15 @@ def rope_store(qkv: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int, q
 
 
 def attention_generic(qkv: torch.Tensor, out: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int,
-                      scale: float, window: Optional[int], tables, kv_view, keys_in_step: bool) -> None:
+                      scale: float, window: Optional[int], tables, kv_view, keys_in_step: bool,
+                      softcap: float = 0.0, slopes: Optional[torch.Tensor] = None) -> None:
     """Causal attention of every row of the step over its sequence's keys. Keys of the
     step's own rows are read from `qkv` when `keys_in_step` is set, earlier ones (or
-    all of them) from the cache."""
+    all of them) from the cache. `softcap` > 0 bounds a score s to softcap * tanh(s / softcap);
+    `slopes` (float32 [heads]) adds slopes[h] * (key position - query position) to head h's scores."""
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.shape != (heads,) or not slopes.is_contiguous()
+                               or slopes.device != qkv.device):
+        raise invalid_argument("attention: the score slopes must be a float32 vector with one entry per head")
     _need_cuda(qkv, out)
     rows = qkv.shape[0]
     if out.shape != (rows, heads * head_dim) or out.dtype != qkv.dtype or out.stride(1) != 1:
@@ -312,7 +318,7 @@ def attention_generic(qkv: torch.Tensor, out: torch.Tensor, *, heads: int, kv_he
         cache_geometry(kv_view, kv_heads, head_dim), out.data_ptr(), out.stride(0),
         tables.row_seq.data_ptr(), tables.row_pos.data_ptr(), tables.seq_slot.data_ptr(),
         tables.seq_start.data_ptr(), tables.seq_row0.data_ptr(), rows, heads, kv_heads, head_dim,
-        int(window or 0), float(scale))
+        int(window or 0), float(scale), float(softcap or 0.0), slopes.data_ptr() if slopes is not None else 0)
     _check(core().kidi_attention_generic(ctypes.byref(args), dtype_code(qkv.dtype), _stream()), "attention")
 
 

@@ -12,7 +12,12 @@ Parameters (`spec.params`): hidden_size, num_heads, num_kv_heads, head_dim, qk_n
 (bool), qk_norm_eps, position (name of a rotary encoding in `env.positions`, or None),
 window (tokens, or None), scale (None: 1/sqrt(head_dim)), qkv_bias and out_bias (bool,
 default false: the reference's Qwen3 projections carry none, src/kidi/layers/qwen3.cpp:14-15;
-its Linear has the option, src/kidi/layers/linear.cpp:181-190).
+its Linear has the option, src/kidi/layers/linear.cpp:181-190), score_softcap (a score s
+becomes cap * tanh(s / cap); default none) and score_slopes (one number per head: head h adds
+slope * (key position - query position) to its scores; default none). The last two have no
+counterpart in the reference's Qwen3; they are there so that an architecture that bounds or
+shifts its scores is a specification, not a change to the kernels' arguments: such layers run
+on the general attention kernel in either precision.
 """
 from __future__ import annotations
 
@@ -64,8 +69,19 @@ class Attention(Part):
         self.qkv: Optional[Linear] = None
         self.out: Optional[Linear] = None
         self.q_norm = self.k_norm = None
+        # Optional: scores bounded by score_softcap * tanh(s / score_softcap); scores of head h shifted by
+        # score_slopes[h] * (key position - query position) (a list with one number per head).
+        self.softcap = float(spec.param("score_softcap", 0.0) or 0.0)
+        slopes = spec.param("score_slopes", None)
+        if slopes is not None and len(slopes) != self.heads:
+            raise invalid_argument("score_slopes needs one number per attention head")
+        if self.softcap < 0:
+            raise invalid_argument("score_softcap must be positive")
+        self.slopes = torch.tensor([float(value) for value in slopes], dtype=torch.float32, device=env.device) \
+            if slopes is not None else None
         self.launcher = AttentionLauncher(heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
-                                          scale=self.scale, window=self.window)
+                                          scale=self.scale, window=self.window, softcap=self.softcap,
+                                          slopes=self.slopes)
 
     def parameter_specs(self) -> List[ParamSpec]:
         specs = [

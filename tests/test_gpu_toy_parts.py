@@ -377,3 +377,71 @@ def test_a_toy_norm_in_a_toy_arrangement(tmp_path, dtype):
     engine = Engine.load(folder, dtype=dtype, max_tokens=2048)
     run_every_way(engine, requests, expected, FP32_TOLERANCE if dtype == "float32" else BF16_TOLERANCE,
                   f"toy norm and arrangement {dtype}")
+
+
+# ------------------------------------------------ scores that are bounded and shifted by position
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_with_bounded_and_shifted_scores(tmp_path, dtype):
+    """The attention part's two options for its scores, set by a specification: layer 0 bounds them
+    (cap * tanh(s / cap)), layer 1 shifts head h's by slope_h * (key position - query position).
+    Nothing in the package's files changes; such layers run on the general attention kernel."""
+    from kidi_b200 import Engine, register_architecture, write_random_model
+    from kidi_b200.models import qwen3
+    from kidi_b200.parts.spec import LayerSpec, PartSpec
+
+    Config = wrapped_config(("cap", "slopes"))
+
+    def build(config):
+        spec = qwen3.build_spec(config.base)
+        extras = ({"score_softcap": config.extra["cap"]}, {"score_slopes": config.extra["slopes"]})
+        layers = []
+        for layer, extra in zip(spec.layers, extras):
+            parts = dict(layer.parts)
+            mixer = parts["mixer"]
+            parts["mixer"] = PartSpec(mixer.kind, dict(mixer.params, **extra), mixer.prefix)
+            layers.append(LayerSpec(layer.arrangement, parts))
+        return dataclasses.replace(spec, architecture="ToyScoresForCausalLM", layers=tuple(layers))
+
+    register_architecture("ToyScoresForCausalLM", Config, build)
+    cap, slopes = 1.5, [0.5, 0.125, 0.03125]
+    raw = dict(BASE, architectures=["ToyScoresForCausalLM"], cap=cap, slopes=slopes)
+    folder = write_random_model(raw, str(tmp_path / "scores"), seed=41, dtype=torch.bfloat16)
+    sharpen_logits(folder)
+    config, tensors = plain_model.read_model_folder(folder)
+    heads, kv_heads, width, eps = 3, 1, 64, config["rms_norm_eps"]
+    cos, sin = plain_model.rotary_tables(320, width, plain_model.rope_theta(config))
+
+    def attention(reshape):
+        def layer(x, prefix):
+            w = lambda name: tensors[prefix + "self_attn." + name].double()
+            n = x.shape[0]
+            q = plain_model.norm_then_rotate((x @ w("q_proj.weight").T).reshape(n, heads, width), w("q_norm.weight"),
+                                             eps, cos[:n].double(), sin[:n].double())
+            k = plain_model.norm_then_rotate((x @ w("k_proj.weight").T).reshape(n, kv_heads, width), w("k_norm.weight"),
+                                             eps, cos[:n].double(), sin[:n].double())
+            v = (x @ w("v_proj.weight").T).reshape(n, kv_heads, width)
+            out = torch.zeros(n, heads, width, dtype=torch.float64)
+            distance = (torch.arange(n)[None, :] - torch.arange(n)[:, None]).double()       # key - query position
+            hidden = distance > 0
+            for head in range(heads):
+                scores = reshape(q[:, head] @ k[:, 0].T / np.sqrt(width), head, distance)
+                scores = scores.masked_fill(hidden, float("-inf"))
+                out[:, head] = torch.softmax(scores, dim=-1) @ v[:, 0]
+            return out.reshape(n, heads * width) @ w("o_proj.weight").T
+        return layer
+
+    bounded = attention(lambda s, head, distance: cap * torch.tanh(s / cap))
+    shifted = attention(lambda s, head, distance: s + slopes[head] * distance)
+
+    def dense(x, prefix):
+        return plain_model.gated_feed_forward(x, tensors, prefix + "mlp.")
+
+    requests = rh.random_requests(config["vocab_size"], [2, 64, 129, 257, 320], seed=42)
+    expected = {name: plain_layers(config, tensors, tokens, [bounded, shifted], [dense, dense])
+                for name, tokens in requests.items()}
+    plain_scores = attention(lambda s, head, distance: s)
+    usual = plain_layers(config, tensors, requests["r2"], [plain_scores, plain_scores], [dense, dense])
+    assert np.abs(usual - expected["r2"]).max() > 1e-2        # the options matter
+    engine = Engine.load(folder, dtype=dtype, max_tokens=2048)
+    run_every_way(engine, requests, expected, FP32_TOLERANCE if dtype == "float32" else BF16_TOLERANCE,
+                  f"bounded and shifted scores {dtype}")
