@@ -119,16 +119,16 @@ def _compile(nvcc: str, source: str, obj: str, flags: Sequence[str]) -> None:
 
 def _remove_older_builds(folder: str, name: str, keep: str) -> None:
     """Drops the shared objects of earlier versions of a library's sources (a process that
-    has one loaded keeps its mapping)."""
-    prefix = f"libkidi_{name}_"
-    for entry in os.listdir(folder):
-        path = os.path.join(folder, entry)
-        stem = entry[len(prefix):-3] if entry.startswith(prefix) and entry.endswith(".so") else ""
-        if path != keep and len(stem) == 16 and all(c in "0123456789abcdef" for c in stem):
-            try:
-                os.remove(path)
-            except OSError:
-                pass
+    has one loaded keeps its mapping) and the lock files left from building them."""
+    kept_tag = os.path.basename(keep)[len(f"libkidi_{name}_"):-3]
+    for prefix, suffix in ((f"libkidi_{name}_", ".so"), (f".{name}_", ".lock")):
+        for entry in os.listdir(folder):
+            stem = entry[len(prefix):-len(suffix)] if entry.startswith(prefix) and entry.endswith(suffix) else ""
+            if stem != kept_tag and len(stem) == 16 and all(c in "0123456789abcdef" for c in stem):
+                try:
+                    os.remove(os.path.join(folder, entry))
+                except OSError:
+                    pass
 
 
 def build_library(name: str, sources: Sequence[str], defines: Optional[Mapping[str, object]] = None,
