@@ -1109,7 +1109,6 @@ __global__ void attention_combine_kernel(Args a) {
 }
 
 constexpr size_t PREFILL_SHARED = (size_t)(TILE + 4 * TILE) * PITCH * sizeof(bf16);
-int kidi_decode_swizzled = 1;
 int kidi_decode_ring = 1;
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1149,7 +1148,6 @@ bool aligned(const Args& a) {
 KIDI_API int kidi_attention_head_dim() { return D; }
 
 // 0: the decode kernel copies pages row by row into padded tiles whatever the head width.
-KIDI_API void kidi_attention_decode_swizzled(int enabled) { kidi_decode_swizzled = enabled; }
 
 // 0: the page-copying decode kernel keeps two key and two value tiles (three blocks of head
 // width 128 an SM) instead of a ring of three tiles (four blocks).
@@ -1158,7 +1156,7 @@ KIDI_API void kidi_attention_decode_ring(int enabled) { kidi_decode_ring = enabl
 // Decode blocks of the kernel for up to eight query heads a key/value head that fit an SM
 // by shared memory (`swizzled`: the cache is one contiguous array and pages are copied whole).
 KIDI_API int kidi_attention_decode_blocks_per_sm(int swizzled) {
-    const size_t block = (swizzled && kidi_decode_swizzled && D % 64 == 0)
+    const size_t block = (swizzled && D % 64 == 0)
                              ? (kidi_decode_ring ? RING_SHARED : SWIZZLED_SHARED) : NARROW_SHARED;
     const int fitting = (int)((228 * 1024) / (block + 1024));       // a kilobyte a block is the system's
     return fitting < 1 ? 1 : fitting > 4 ? 4 : fitting;             // four by registers
@@ -1209,7 +1207,7 @@ KIDI_API int kidi_attention_decode(const Args* args, cudaStream_t stream) {
     if (clustered && (group > 8 || a.splits > 8)) return KIDI_REFUSED_SIZE;
     if (a.splits > 1 && !clustered && (!a.partial_out || !a.partial_stat)) return KIDI_REFUSED_SIZE;
     // Head widths that are multiples of 64 take whole pages by TMA tensor copies.
-    const bool swizzled = kidi_decode_swizzled && group <= 8 && D % 64 == 0 && a.cache_rows > 0;
+    const bool swizzled = group <= 8 && D % 64 == 0 && a.cache_rows > 0;
     CUtensorMap k_map, v_map;
     memset(&k_map, 0, sizeof(k_map));
     memset(&v_map, 0, sizeof(v_map));

@@ -23,9 +23,6 @@ FORCE_GENERIC = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1"
 # One token per sequence: the decode kernel normalises and rotates q and the new key itself and
 # writes the new key and value to the cache (one kernel less per layer); 0 switches that off.
 FUSE_ROTATION = os.environ.get("KIDI_B200_FUSE_ROTATION", "1") == "1"
-# Head widths that are multiples of 64: the decode kernel takes whole pages by TMA tensor copies
-# (False, for tests of the other form at such a width: row by row into padded tiles).
-DECODE_SWIZZLED = True
 # The page-copying decode kernel keeps a ring of three tiles (keys and values in turn), so that
 # four blocks of head width 128 fit an SM (0: two key and two value tiles, three blocks).
 # "force": wherever the kernel has that form (for tests of it on small batches).
@@ -64,9 +61,6 @@ def library(head_dim: int) -> ctypes.CDLL:
         lib.kidi_attention_prefill.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_attention_decode.argtypes = [c_void_p, c_void_p]
         lib.kidi_attention_prefill.restype = lib.kidi_attention_decode.restype = c_int
-        lib.kidi_attention_decode_swizzled.argtypes = [c_int]
-        lib.kidi_attention_decode_swizzled.restype = None
-        lib.kidi_attention_decode_swizzled(1 if DECODE_SWIZZLED else 0)
         lib.kidi_attention_decode_ring.argtypes = [c_int]
         lib.kidi_attention_decode_ring.restype = None
         lib.kidi_attention_decode_ring(0)
@@ -150,7 +144,7 @@ def sm_count(device: torch.device) -> int:
 
 
 def ring_available(head_dim: int) -> bool:
-    return DECODE_SWIZZLED and DECODE_RING and head_dim % 64 == 0
+    return DECODE_RING and head_dim % 64 == 0
 
 
 def blocks_per_sm(head_dim: int = 128, ring: bool = False) -> int:

@@ -12,7 +12,6 @@ DEVICE = torch.device("cuda:0")     # only its index is used: the SM count is gi
 @pytest.fixture(autouse=True)
 def a_b200(monkeypatch):
     monkeypatch.setitem(attention._sm_count, 0, 148)
-    monkeypatch.setattr(attention, "DECODE_SWIZZLED", True)
     monkeypatch.setattr(attention, "DECODE_RING", True)
     monkeypatch.setattr(attention, "DECODE_RING_ALWAYS", False)
     monkeypatch.delenv("KIDI_B200_DECODE_SPLITS", raising=False)
