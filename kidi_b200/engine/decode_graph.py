@@ -26,12 +26,12 @@ graph is captured once): a part that is to run in a captured step reads `ctx.tab
 from __future__ import annotations
 
 import gc
-from typing import Dict, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 
-from ..errors import KidiError, invalid_argument
+from ..errors import invalid_argument
 from ..kernels import ops
 from .plan import StepPlan
 

@@ -11,16 +11,13 @@ only when everything succeeded).
 """
 from __future__ import annotations
 
-import dataclasses
-import time
-from typing import Any, Dict, List, Mapping, Optional, Sequence
+from typing import Any, Dict, Mapping, Optional, Sequence
 
-import numpy as np
 import torch
 
 from ..cache.sequence_cache import SequenceCache
 from ..config.reader import read_config_json
-from ..errors import KidiError, invalid_argument, runtime_error
+from ..errors import invalid_argument, runtime_error
 from ..kernels import attention as attention_kernels
 from ..registry import spec_from_config
 from ..weights.loader import Checkpoint, TensorDict, bind_parameters

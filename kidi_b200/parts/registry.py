@@ -7,7 +7,7 @@ in a `ModelSpec` without touching this package.
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, Type
+from typing import Callable, Dict
 
 from ..errors import unsupported
 from .spec import PartSpec

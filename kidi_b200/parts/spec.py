@@ -14,7 +14,7 @@ The reference keeps the same separation with constructor parameters
 from __future__ import annotations
 
 import dataclasses
-from typing import Any, Dict, Mapping, Optional, Sequence, Tuple
+from typing import Any, Mapping, Optional, Sequence, Tuple
 
 
 @dataclasses.dataclass(frozen=True)

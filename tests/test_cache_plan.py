@@ -2,7 +2,6 @@
 or freed twice; groups with storage of their own; rings; fixed-size state."""
 import random
 
-import numpy as np
 import pytest
 import torch
 

@@ -8,7 +8,7 @@ from kidi_b200 import ErrorCode, KidiError, register_architecture, registered_ar
 from kidi_b200.config.qwen3 import Qwen3Config
 from kidi_b200.config.reader import read_config_json
 from kidi_b200.registry import resolve_architecture, spec_from_config
-from tiny_configs import ALL, TINY_A, TINY_B, TINY_C
+from tiny_configs import ALL, TINY_A, TINY_B
 
 
 def code_of(callable_, *args):

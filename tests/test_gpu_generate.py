@@ -6,10 +6,8 @@ import os
 
 import numpy as np
 import pytest
-import torch
 
 import plain_model
-from tiny_configs import ALL, TINY_A, TINY_B
 
 pytestmark = pytest.mark.gpu
 

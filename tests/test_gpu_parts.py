@@ -2,7 +2,6 @@
 lets a layer read another layer's cache, and a toy mixer with state of its own that is
 registered, built, loaded and stepped without a change to the package."""
 import dataclasses
-import math
 
 import numpy as np
 import pytest

@@ -9,7 +9,6 @@ import sys
 
 import numpy as np
 import pytest
-import torch
 
 import replay_helpers as rh
 from tiny_configs import ALL

@@ -200,7 +200,6 @@ def test_weight_rules_rename_split_transpose_identical_and_ignore():
 def test_parts_name_tensors_they_ignore():
     """A part's own `ignored_tensors` (relative to its prefix) reach the loader through the model."""
     from kidi_b200.engine.model import CausalLM
-    from kidi_b200.parts.attention import Attention
     model = CausalLM(spec_from_config(TINY_A)[2], torch.bfloat16, CPU)
     assert model.ignored_tensors() == []
     mixer = model.layers[1].mixer
