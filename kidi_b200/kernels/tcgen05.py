@@ -7,7 +7,8 @@ double-buffered in tensor memory, results written by TMA stores. With few rows t
 product is bound by reading the weight once; the kernel then deals the k-blocks of the
 tiles out over all blocks, which needs a workspace and counters that this module keeps
 per device (allocated once, never replaced, so that captured graphs can hold their
-addresses).
+addresses). Products of one device therefore must not overlap in time: the package issues
+all its work on one stream; a caller with streams of its own orders the calls.
 
 KIDI_B200_TCGEN05_MAX_ROWS bounds the rows for which `fits` says yes (0 switches the
 kernel off); above it the caller uses the matrix library, which streams weights faster
