@@ -155,10 +155,10 @@ struct Params {
 // tiles (see `locate`). With a tile for every block, block b takes whole tiles b,
 // b + blocks, ... and writes their results to y. With fewer tiles than blocks (few tokens: the
 // product is bound by reading the weights once) the tiles' k-blocks form one line, tile after
-// tile, of which every block takes an equal, contiguous piece; the blocks being a multiple of
-// the tiles, that is split-K. A piece's parts of tiles go to the workspace; the block that
-// brings a tile's last part adds all parts in their order along k, so the result does not
-// depend on timing.
+// tile, of which every block takes an equal, contiguous piece (split-K; a piece may end one tile
+// and begin the next). A piece's parts of tiles go to the workspace; when all parts of a tile are
+// there, every block that brought one adds its share of the tile's token columns over all parts,
+// in their order along k, so the result does not depend on timing.
 // A block keeps its ring of operand stages full across the borders of tiles, and the accumulator
 // is double-buffered in tensor memory (2 x BN columns): while the four epilogue warps read one
 // piece of work out, the tensor core is at the next.
