@@ -135,6 +135,15 @@ class StateGroup:
 
 
 @dataclasses.dataclass(frozen=True)
+class StateSnapshot:
+    """The fixed-size state of one slot at one length (see `SequenceCache.snapshot_state`)."""
+
+    slot: int
+    length: int
+    tensors: list
+
+
+@dataclasses.dataclass(frozen=True)
 class KVView:
     """What one schedule entry's mixer sees of the cache."""
 
@@ -283,13 +292,24 @@ class SequenceCache:
         for slot, length in growth:
             self.lengths[slot] = length
 
-    def rewind(self, slot: int, length: int) -> None:
+    def snapshot_state(self, slot: int) -> "StateSnapshot":
+        """A copy of the slot's fixed-size state (every state group) as it is now, with the
+        sequence's length: what `rewind` needs to come back to this point (keys and values
+        need none: their rows beyond the length are simply forgotten)."""
+        return StateSnapshot(slot, self.length(slot), [group.storage[:, slot].clone() for group in self.state_groups])
+
+    def rewind(self, slot: int, length: int, state: Optional["StateSnapshot"] = None) -> None:
         """Forgets tokens beyond `length` (the reference's rewind moves the position,
         src/kidi/model/gemma4.cpp:545-560). Full-history groups give pages back; a ring
-        cannot be rewound past what it overwrote."""
+        cannot be rewound past what it overwrote. Fixed-size state cannot be computed
+        backwards: a model that has some is rewound to a point of which `state` is the
+        snapshot (`snapshot_state`, taken at that length)."""
         current = self.length(slot)
         if length < 0 or length > current:
             raise invalid_argument(f"cannot rewind slot {slot} from {current} to {length}")
+        if state is not None and (state.slot != slot or state.length != length or
+                                  len(state.tensors) != len(self.state_groups)):
+            raise invalid_argument("the state snapshot is not of this slot at this length")
         for group in self.kv_groups:
             if group.ring_pages and current > group.ring_tokens and length < current:
                 raise invalid_argument("a windowed cache that has wrapped cannot be rewound")
@@ -298,7 +318,11 @@ class SequenceCache:
             group.pool.release_many(held[keep:])
             del held[keep:]
         if self.state_groups and length < current:
-            raise invalid_argument("fixed-size per-sequence state cannot be rewound")
+            if state is None:
+                raise invalid_argument("fixed-size per-sequence state cannot be rewound without a snapshot "
+                                       "taken at the length to return to")
+            for group, saved in zip(self.state_groups, state.tensors):
+                group.storage[:, slot].copy_(saved)
         self.lengths[slot] = length
 
     def flush_tables(self) -> None:

@@ -140,6 +140,33 @@ def test_rewind():
         cache.rewind(slot, 71)
 
 
+def test_rewind_with_fixed_size_state_takes_a_snapshot():
+    cache = make_cache(requests=[[KVRequest(1, 16), StateRequest((2, 3))], [StateRequest((2, 3))]])
+    slot, other = cache.acquire(), cache.acquire()
+    state = [cache.views(0)[1], cache.views(1)[0]]
+    cache.reserve([(slot, 100)])
+    cache.commit([(slot, 100)])
+    state[0][slot].fill_(1.0)
+    state[1][slot].fill_(2.0)
+    state[0][other].fill_(9.0)
+    saved = cache.snapshot_state(slot)                      # the state after 100 tokens
+    cache.reserve([(slot, 180)])
+    cache.commit([(slot, 180)])
+    state[0][slot].fill_(3.0)
+    state[1][slot].fill_(4.0)
+    with pytest.raises(KidiError):
+        cache.rewind(slot, 100)                             # state cannot be computed backwards
+    with pytest.raises(KidiError):
+        cache.rewind(slot, 90, state=saved)                 # the snapshot is of another length
+    with pytest.raises(KidiError):
+        cache.rewind(other, 0, state=saved)                 # and of another slot
+    cache.rewind(slot, 100, state=saved)
+    assert cache.length(slot) == 100 and len(cache.kv_groups[0].pages[slot]) == 2
+    assert float(state[0][slot].mean()) == 1.0 and float(state[1][slot].mean()) == 2.0
+    assert float(state[0][other].mean()) == 9.0             # nobody else's state moved
+    cache.check()
+
+
 def test_the_budget_counts_whole_pages():
     cache = make_cache(max_tokens=130, requests=[[KVRequest(1, 16)]])
     assert cache.max_tokens == 192 and cache.n_slots == 3
